@@ -39,7 +39,8 @@ class CacheGroup:
     v: Optional[torch.Tensor] = None
 
     def bytes_per_page(self, page_size: int, itemsize: int) -> int:
-        return 2 * len(self.layers) * page_size * self.need.num_kv_heads * self.need.head_dim * itemsize
+        tensors = 1 if self.need.shared_kv else 2
+        return tensors * len(self.layers) * page_size * self.need.num_kv_heads * self.need.head_dim * itemsize
 
 
 class PageTable:
@@ -137,7 +138,7 @@ class CacheManager:
         for g, grp in enumerate(self.groups):
             shape = (len(grp.layers), self.num_pages, self.page_size, grp.need.num_kv_heads, grp.need.head_dim)
             grp.k = torch.zeros(shape, dtype=dtype, device=device)
-            grp.v = torch.zeros(shape, dtype=dtype, device=device)
+            grp.v = grp.k if grp.need.shared_kv else torch.zeros(shape, dtype=dtype, device=device)
             for i, layer in enumerate(grp.layers):
                 views[layer] = PagedLayerCache(group=g, k=grp.k[i], v=grp.v[i])
         for layer, need in self.state_layers.items():

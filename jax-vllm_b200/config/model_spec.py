@@ -54,14 +54,71 @@ class GatedMLPSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose keys and values are made from one low-rank latent per token: a query head is
+    [plain_dim | rot_dim]; a token leaves a normed latent of `latent_dim` and one rotated key part of `rot_dim`
+    that all heads share; head h's key is [W_uk_h latent | rotated part], its value W_uv_h latent."""
+    hidden_size: int
+    num_heads: int
+    plain_dim: int                 # query/key elements of a head that are not rotated
+    rot_dim: int                   # rotated elements of a head (the shared key part has this size)
+    value_dim: int
+    latent_dim: int
+    scale: float
+    position: Optional[Any] = None  # rotation of the rot_dim part, or None
+    latent_norm_eps: float = 1e-6  # RMSNorm of the latent
+    output_gate: bool = False      # heads multiplied by sigmoid(W_g x) before the output projection
+    prefix: str = "self_attn"
+    # tensor names below the prefix: queries, down-projection (latent | key part), latent norm, key and value
+    # up-projections, gate, output
+    names: tuple = ("q", "dkv", "dkv.norm", "uk", "uv", "g", "o")
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """A mixture of small feed-forward experts down(act(up(x))): each token uses the `top_k` experts with the
+    largest router scores; with `n_groups` > 1 the experts form equal groups of neighbours, a group scores as
+    its best expert, and only experts of the `keep_groups` best groups can be chosen."""
+    hidden_size: int
+    num_experts: int
+    top_k: int
+    expert_size: int
+    n_groups: int = 1
+    keep_groups: int = 1
+    scoring: str = "softmax"       # router scores: softmax over all experts
+    renormalize: bool = False      # whether the chosen scores are made to sum to one
+    activation: str = "gelu"       # exact (erf) gelu
+    prefix: str = "mlp"
+    kind: str = "routed_experts"
+
+
+@dataclass(frozen=True)
+class TokenInputSpec:
+    """A per-layer input that depends on the token id: e = columns [offset, offset + dim) of a shared table
+    row; branch = proj(gelu_tanh(gate(x)) * e), normed by an RMSNorm of its own."""
+    hidden_size: int
+    dim: int
+    offset: int                    # first column of this layer's part of a table row
+    table_name: str                # full tensor name of the table [vocab, table_width]
+    table_width: int
+    vocab_size: int
+    eps: float
+    prefix: str = "side"
+    kind: str = "token_input"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     prefix: str                    # e.g. "model.layers.3"
     mixer: Any
-    feed_forward: Any
+    feed_forward: Any              # None: the layer has no feed-forward (arrangements that allow it)
     mixer_norm: NormSpec
-    ffn_norm: NormSpec
+    ffn_norm: Optional[NormSpec]
     cache_from: Optional[int] = None
     kind: str = "pre_norm"
+    residual_scale: float = 1.0    # multiplies every branch before it is added to the stream
+    token_input: Any = None        # a further branch fed by the token id (TokenInputSpec), or None
 
 
 @dataclass(frozen=True)

@@ -31,7 +31,7 @@ struct AttnParams {
   const int* block_table; int table_width;
   const int* cu_seqlens; const int* start_pos;
   const int* work;  // [n_work][2] = (entry, q_off)
-  int n_q_heads, n_kv_heads, head_dim, page_size, num_pages, window;
+  int n_q_heads, n_kv_heads, head_dim, v_dim, page_size, num_pages, window;
   float scale;
   int tokens_per_tile, heads_per_tile, n_head_groups, split_size, n_splits;
   int* status;
@@ -41,10 +41,11 @@ template <typename T, bool SPLIT>
 __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) {
   extern __shared__ float smem[];
   const int D = p.head_dim;
+  const int DV = p.v_dim;                          // leading elements of a value row that are used (<= D)
   float* Qs = smem;                                // [BLOCK_M][D]
   float* Ks = Qs + BLOCK_M * D;                    // [BLOCK_N][D+1]
-  float* Vs = Ks + BLOCK_N * (D + 1);              // [BLOCK_N][D]
-  float* Ss = Vs + BLOCK_N * D;                    // [BLOCK_M][BLOCK_N]
+  float* Vs = Ks + BLOCK_N * (D + 1);              // [BLOCK_N][DV]
+  float* Ss = Vs + BLOCK_N * DV;                   // [BLOCK_M][BLOCK_N]
   float* row_m = Ss + BLOCK_M * BLOCK_N;           // [BLOCK_M]
   float* row_l = row_m + BLOCK_M;                  // [BLOCK_M]
   float* row_alpha = row_l + BLOCK_M;              // [BLOCK_M]
@@ -90,7 +91,7 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
     Qs[idx] = v;
   }
 
-  constexpr int DC = 2;  // output columns per thread: d = tid, tid + THREADS  (head_dim <= 256)
+  constexpr int DC = 4;  // output columns per thread: d = tid, tid + THREADS, ...  (v_dim <= 512)
   float acc[BLOCK_M][DC];
 #pragma unroll
   for (int m = 0; m < BLOCK_M; ++m)
@@ -115,10 +116,8 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
           vrow = vc + off;
         }
       }
-      for (int d = lane; d < D; d += 32) {
-        Ks[n * (D + 1) + d] = krow ? to_f32(krow[d]) : 0.f;
-        Vs[n * D + d] = vrow ? to_f32(vrow[d]) : 0.f;
-      }
+      for (int d = lane; d < D; d += 32) Ks[n * (D + 1) + d] = krow ? to_f32(krow[d]) : 0.f;
+      for (int d = lane; d < DV; d += 32) Vs[n * DV + d] = vrow ? to_f32(vrow[d]) : 0.f;
     }
     __syncthreads();
 
@@ -163,11 +162,11 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
 #pragma unroll
     for (int c = 0; c < DC; ++c) {
       const int d = tid + c * THREADS;
-      if (d < D) {
+      if (d < DV) {
 #pragma unroll
         for (int m = 0; m < BLOCK_M; ++m) acc[m][c] *= row_alpha[m];
         for (int n = 0; n < BLOCK_N; ++n) {
-          const float v = Vs[n * D + d];
+          const float v = Vs[n * DV + d];
 #pragma unroll
           for (int m = 0; m < BLOCK_M; ++m) acc[m][c] = fmaf(Ss[m * BLOCK_N + n], v, acc[m][c]);
         }
@@ -180,7 +179,7 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
 #pragma unroll
   for (int c = 0; c < DC; ++c) {
     const int d = tid + c * THREADS;
-    if (d >= D) continue;
+    if (d >= DV) continue;
 #pragma unroll
     for (int m = 0; m < BLOCK_M; ++m) {
       if (row_pos[m] < 0) continue;
@@ -190,13 +189,13 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
       if (SPLIT) {
         // rows of split launches are single tokens: index by work item
         const size_t slot = ((size_t)blockIdx.x * p.n_q_heads + head) * p.n_splits + blockIdx.z;
-        p.part_o[slot * D + d] = acc[m][c];
+        p.part_o[slot * DV + d] = acc[m][c];
         if (d == 0) {
           p.part_ml[slot * 2] = row_m[m];
           p.part_ml[slot * 2 + 1] = row_l[m];
         }
       } else {
-        ((T*)p.out)[token * p.out_stride + (size_t)head * D + d] = from_f32<T>(acc[m][c] / row_l[m]);
+        ((T*)p.out)[token * p.out_stride + (size_t)head * DV + d] = from_f32<T>(acc[m][c] / row_l[m]);
       }
     }
   }
@@ -207,7 +206,7 @@ template <typename T>
 __global__ void attn_combine_kernel(const AttnParams p) {
   const int x = blockIdx.x, head = blockIdx.y;
   const int entry = p.work[2 * x];
-  const int D = p.head_dim;
+  const int D = p.v_dim;
   const int pos = p.start_pos[entry];
   const int j_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
   const int j_hi = pos + 1;
@@ -232,8 +231,8 @@ __global__ void attn_combine_kernel(const AttnParams p) {
   }
 }
 
-size_t smem_bytes(int D) {
-  return sizeof(float) * ((size_t)BLOCK_M * D + (size_t)BLOCK_N * (D + 1) + (size_t)BLOCK_N * D +
+size_t smem_bytes(int D, int DV) {
+  return sizeof(float) * ((size_t)BLOCK_M * D + (size_t)BLOCK_N * (D + 1) + (size_t)BLOCK_N * DV +
                           BLOCK_M * BLOCK_N + 3 * BLOCK_M) + sizeof(int) * BLOCK_M;
 }
 }  // namespace
@@ -249,6 +248,8 @@ JV_EXPORT int jv_attn_simt_tokens_per_tile(int n_q_heads, int n_kv_heads) {
 // k_cache/v_cache: [num_pages, page_size, n_kv_heads, head_dim]; block_table: [entries, table_width];
 // cu_seqlens: [entries+1]; start_pos: [entries] (tokens cached before this step); work:
 // [n_work, 2] int32 (entry, first token of the tile within the entry's new tokens).
+// v_dim: how many leading elements of a value row are used (0: all head_dim); out and part_o then have v_dim
+// elements per head.  A cache whose values are the leading part of its keys passes the same tensor twice.
 // n_splits == 0: every work item attends to its whole visible range and writes `out`.
 // n_splits > 0: work items are single tokens; part_o [n_work*Hq*n_splits*D] and part_ml
 // [n_work*Hq*n_splits*2] floats are scratch; a second launch merges into `out`.
@@ -257,17 +258,19 @@ JV_EXPORT int jv_attn_simt(const void* q, int q_stride, void* out, int out_strid
                            const int* block_table, int table_width, const int* cu_seqlens,
                            const int* start_pos, const int* work, int n_work, int n_q_heads,
                            int n_kv_heads, int head_dim, int page_size, int num_pages, int window,
-                           float scale, int split_size, int n_splits, int* status,
+                           float scale, int split_size, int n_splits, int v_dim, int* status,
                            cudaStream_t stream) {
   if (n_work == 0) return JV_OK;
-  if (head_dim < 1 || head_dim > 256 || n_kv_heads < 1 || n_q_heads % n_kv_heads != 0)
+  if (v_dim <= 0) v_dim = head_dim;
+  if (head_dim < 1 || v_dim > head_dim || v_dim > 512 || smem_bytes(head_dim, v_dim) > 227 * 1024 || n_kv_heads < 1 ||
+      n_q_heads % n_kv_heads != 0)
     return JV_ERR_UNSUPPORTED;
   AttnParams p;
   p.q = q; p.q_stride = q_stride; p.out = out; p.out_stride = out_stride;
   p.part_o = part_o; p.part_ml = part_ml; p.k_cache = k_cache; p.v_cache = v_cache;
   p.block_table = block_table; p.table_width = table_width; p.cu_seqlens = cu_seqlens;
   p.start_pos = start_pos; p.work = work; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
-  p.head_dim = head_dim; p.page_size = page_size; p.num_pages = num_pages; p.window = window;
+  p.head_dim = head_dim; p.v_dim = v_dim; p.page_size = page_size; p.num_pages = num_pages; p.window = window;
   p.scale = scale; p.status = status;
   const int G = n_q_heads / n_kv_heads;
   p.heads_per_tile = G < BLOCK_M ? G : BLOCK_M;
@@ -275,7 +278,7 @@ JV_EXPORT int jv_attn_simt(const void* q, int q_stride, void* out, int out_strid
   p.n_head_groups = (G + p.heads_per_tile - 1) / p.heads_per_tile;
   p.split_size = split_size > 0 ? split_size : 1;
   p.n_splits = n_splits;
-  const size_t smem = smem_bytes(head_dim);
+  const size_t smem = smem_bytes(head_dim, v_dim);
   dim3 grid(n_work, n_kv_heads * p.n_head_groups, n_splits > 0 ? n_splits : 1);
   int rc = JV_OK;
   JV_DISPATCH_DTYPE(dtype, T, {

@@ -12,7 +12,11 @@ template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(256) gemm_tn_simt_kernel(const TA* __restrict__ A, int lda,
                                                            const TW* __restrict__ W, int ldw,
                                                            TC* __restrict__ C, int ldc, int M, int N,
-                                                           int K) {
+                                                           int K, size_t a_batch = 0, size_t w_batch = 0,
+                                                           size_t c_batch = 0) {
+  A += blockIdx.z * a_batch;      // a batch of independent products: grid.z of them, operands this far apart
+  W += blockIdx.z * w_batch;
+  C += blockIdx.z * c_batch;
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -75,6 +79,21 @@ JV_EXPORT int jv_gemm_tn_simt(const void* A, int a_dtype, int lda, const void* W
   if (grid.y > 65535) return JV_ERR_UNSUPPORTED;
   JV_DISPATCH_DTYPE(a_dtype, TA, JV_DISPATCH_DTYPE(w_dtype, TW, JV_DISPATCH_DTYPE(c_dtype, TC,
       (gemm_tn_simt_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>(
-          (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K)))));
+          (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, 0, 0, 0)))));
+  return jv_check_launch();
+}
+
+// `batch` products of the same sizes in one launch: product b reads A + b*a_batch, W + b*w_batch and writes
+// C + b*c_batch (strides in elements; rows of one product may lie between rows of another).
+JV_EXPORT int jv_gemm_tn_simt_batched(const void* A, int a_dtype, int lda, long long a_batch, const void* W, int w_dtype,
+                                      int ldw, long long w_batch, void* C, int c_dtype, int ldc, long long c_batch,
+                                      int M, int N, int K, int batch, cudaStream_t stream) {
+  if (M == 0 || N == 0 || batch == 0) return JV_OK;
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batch);
+  if (grid.y > 65535 || batch > 65535) return JV_ERR_UNSUPPORTED;
+  JV_DISPATCH_DTYPE(a_dtype, TA, JV_DISPATCH_DTYPE(w_dtype, TW, JV_DISPATCH_DTYPE(c_dtype, TC,
+      (gemm_tn_simt_kernel<TA, TW, TC><<<grid, 256, 0, stream>>>(
+          (const TA*)A, lda, (const TW*)W, ldw, (TC*)C, ldc, M, N, K, (size_t)a_batch, (size_t)w_batch,
+          (size_t)c_batch)))));
   return jv_check_launch();
 }

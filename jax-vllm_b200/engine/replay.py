@@ -32,7 +32,7 @@ from .batch import StepEntry
 from .loading import load_from_path
 from .runner import Runner
 
-MAX_LIVE = 8
+MAX_LIVE = 4          # state slots: no more requests than this are live at a time
 
 
 class Replayer:

@@ -52,6 +52,35 @@ class PartialSum:
         return out if dtype == torch.float32 else out.to(dtype)
 
 
+class PickedRows:
+    """A result [n, width] given as rows of `rows` [m, width] to be picked and weighted: row r of the result is
+    sum_s coef[r, s] * rows[pick[r, s]] (32-bit, s ascending): what a routed feed-forward leaves (its experts'
+    outputs in the order of the experts, and for every token where its chosen experts' rows are and what they
+    weigh).  `branch_norm_add` adds the rows up as it reads them; `tensor()` does it for any other reader."""
+
+    def __init__(self, rows: torch.Tensor, pick: torch.Tensor, coef: torch.Tensor):
+        self.rows, self.pick, self.coef = rows, pick, coef
+
+    @property
+    def shape(self):
+        return (self.pick.shape[0], self.rows.shape[1])
+
+    @property
+    def device(self):
+        return self.rows.device
+
+    def tensor(self, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        _cuda(self.rows, "rows"); _cuda(self.pick, "pick", torch.int32); _cuda(self.coef, "coef", torch.float32)
+        n, width = self.shape
+        out = torch.empty((n, width), dtype=torch.float32, device=self.device)
+        f = _fn("branch_norm", "jv_pick_rows_sum", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int,
+                                                    c_int, c_void_p, c_void_p])
+        _check(f(self.rows.data_ptr(), _code(self.rows, "rows"), self.pick.data_ptr(), self.coef.data_ptr(),
+                 self.pick.shape[1], self.rows.shape[0], out.data_ptr(), n, width, _status_ptr(self.device), _stream()),
+               "pick_rows_sum")
+        return out if dtype == torch.float32 else out.to(dtype)
+
+
 _fn_cache: dict[tuple[str, str], object] = {}
 launch_count = 0     # kernels of this package launched so far (library products are not counted)
 _status: dict[int, torch.Tensor] = {}
@@ -251,6 +280,8 @@ def _delta_parts(delta, h: torch.Tensor):
     """(tensor, parts, elements between parts) for a `delta` that is a tensor, a PartialSum or None."""
     if delta is None:
         return None, 1, 0
+    if isinstance(delta, PickedRows):
+        delta = delta.tensor()
     if isinstance(delta, PartialSum):
         parts = _cuda(delta.parts, "delta parts", torch.float32)
         if tuple(parts.shape[1:]) != tuple(h.shape):
@@ -351,10 +382,12 @@ def attn_simt_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
 def attn_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor,
               n_work: int, n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
-              split_size: int = 0, n_splits: int = 0) -> None:
+              split_size: int = 0, n_splits: int = 0, v_dim: int = 0) -> None:
     """Paged causal attention on CUDA cores (csrc/attn_simt.cu).  `work` is [n_work, 2] int32
     (entry, first token of the tile); with `n_splits` > 0 the work items are single tokens
-    whose keys are split into `n_splits` ranges of `split_size` positions."""
+    whose keys are split into `n_splits` ranges of `split_size` positions.  `v_dim` > 0: only that many
+    leading elements of a value row are used and `out` has v_dim elements per head (a cache whose values are
+    the leading part of its keys is passed as both caches)."""
     for t, nm in ((q, "q"), (out, "out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
         _cuda(t, nm, q.dtype, contiguous=(nm != "q"))
     for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (work, "work")):
@@ -363,16 +396,16 @@ def attn_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
         return
     part_o = part_ml = None
     if n_splits > 0:
-        part_o = torch.empty(n_work * n_q_heads * n_splits * head_dim, dtype=torch.float32, device=q.device)
+        part_o = torch.empty(n_work * n_q_heads * n_splits * (v_dim or head_dim), dtype=torch.float32, device=q.device)
         part_ml = torch.empty(n_work * n_q_heads * n_splits * 2, dtype=torch.float32, device=q.device)
     f = _fn("attn_simt", "jv_attn_simt", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                          c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p,
+                                          c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
                                           c_void_p])
     _check(f(q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), _code(q, "q"), _ptr(part_o), _ptr(part_ml),
              k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
              cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads, n_kv_heads, head_dim,
-             k_cache.shape[1], k_cache.shape[0], int(window), float(scale), int(split_size), int(n_splits),
+             k_cache.shape[1], k_cache.shape[0], int(window), float(scale), int(split_size), int(n_splits), int(v_dim),
              _status_ptr(q.device), _stream()), "attn_simt", launches=2 if n_splits > 0 else 1)
 
 
@@ -748,6 +781,223 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     if out_dtype == torch.bfloat16:
         return torch.mm(x, weight.t())
     return torch.mm(x, weight.t(), out_dtype=out_dtype)
+
+
+# ------------------------------------------------- layers that norm a branch's output
+def branch_norm_add(h: torch.Tensor, branch, weight: torch.Tensor, eps: float, mult: float,
+                    x_dtype: torch.dtype | None = None) -> torch.Tensor | None:
+    """h += mult * rmsnorm(branch) * weight, in 32-bit and in place (csrc/branch_norm.cu); returns h rounded to
+    `x_dtype` (what the next branch reads), or None if no `x_dtype` is given.  `branch` is a tensor [n, hidden], a
+    PartialSum or a PickedRows; the latter two are added up as they are read."""
+    _cuda(h, "h", torch.float32); _cuda(weight, "weight")
+    pick = coef = None
+    if isinstance(branch, PickedRows):
+        branch, pick, coef = branch.rows, branch.pick, branch.coef
+    n, hidden = h.shape
+    if weight.shape != (hidden,):
+        raise KernelError(f"norm weight has shape {tuple(weight.shape)}, rows have {hidden} elements")
+    parts, part_stride, y_rows = 1, 0, n
+    if pick is not None:
+        _cuda(pick, "pick", torch.int32); _cuda(coef, "coef", torch.float32); _cuda(branch, "branch")
+        if pick.shape != coef.shape or pick.shape[0] != n or branch.shape[1] != hidden:
+            raise KernelError("pick, coef and branch do not fit the stream")
+        parts, y_rows, y = pick.shape[1], branch.shape[0], branch
+    else:
+        y, parts, part_stride = _delta_parts(branch, h)
+    x = torch.empty((n, hidden), dtype=x_dtype, device=h.device) if x_dtype is not None else None
+    f = _fn("branch_norm", "jv_branch_norm_add", [c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_int,
+                                                  c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_float,
+                                                  c_void_p, c_void_p])
+    _check(f(h.data_ptr(), y.data_ptr(), _code(y, "branch"), part_stride, parts, _ptr(pick), _ptr(coef), y_rows,
+             weight.data_ptr(), _code(weight, "weight"), _ptr(x), 0 if x is None else _code(x, "x"), n, hidden,
+             float(eps), float(mult), _status_ptr(h.device), _stream()), "branch_norm_add")
+    return x
+
+
+def cast_rows(h: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """The float32 stream rounded to `dtype` (the stream itself for float32)."""
+    _cuda(h, "h", torch.float32)
+    if dtype == torch.float32:
+        return h
+    x = torch.empty_like(h, dtype=dtype)
+    f = _fn("branch_norm", "jv_cast_rows", [c_void_p, c_void_p, c_int, c_longlong, c_void_p])
+    _check(f(h.data_ptr(), x.data_ptr(), _code(x, "x"), h.numel(), _stream()), "cast_rows")
+    return x
+
+
+# ------------------------------------------------------------------ latent attention
+def latent_prepare(row: torch.Tensor, q_off: int, kv_off: int, q_latent: torch.Tensor | None, q_out: torch.Tensor,
+                   positions: torch.Tensor, token_entry: torch.Tensor, block_table: torch.Tensor,
+                   inv_freq: torch.Tensor | None, norm_w: torch.Tensor | None, eps: float, cache: torch.Tensor | None,
+                   heads: int, plain_dim: int, rot_dim: int, latent_dim: int) -> None:
+    """Writes a token's cache row [normed latent | rotated key part] and puts its query row together as
+    [q_latent | rotated query part] per head (csrc/latent_prepare.cu).  `row`: the product rows
+    [queries | down-projection]; `kv_off` < 0 or `cache` None: queries only.  `q_latent` [heads, n, latent_dim]
+    is copied into `q_out` if given (else it is there already)."""
+    _cuda(row, "row", contiguous=False); _cuda(q_out, "q_out", row.dtype)
+    _cuda(positions, "positions", torch.int32); _cuda(token_entry, "token_entry", torch.int32)
+    _cuda(block_table, "block_table", torch.int32)
+    n = row.shape[0]
+    dk = latent_dim + rot_dim
+    if q_out.shape != (n, heads * dk):
+        raise KernelError(f"q_out has shape {tuple(q_out.shape)}, expected {(n, heads * dk)}")
+    if inv_freq is not None:
+        _cuda(inv_freq, "inv_freq", torch.float32)
+        if 2 * inv_freq.numel() != rot_dim:
+            raise KernelError("the rotation table does not fit the rotated part")
+    if q_latent is not None:
+        _cuda(q_latent, "q_latent", row.dtype)
+        if q_latent.shape != (heads, n, latent_dim):
+            raise KernelError("q_latent must be [heads, n, latent_dim]")
+    writes = cache is not None and kv_off >= 0
+    page_size = num_pages = 1
+    if writes:
+        _cuda(cache, "cache", row.dtype); _cuda(norm_w, "latent norm weight")
+        if cache.shape[2:] != (1, dk) or norm_w.shape != (latent_dim,):
+            raise KernelError(f"cache shape {tuple(cache.shape)} does not fit rows of {dk}")
+        if row.shape[1] < kv_off + dk:
+            raise KernelError("the product row is too short for the down-projection")
+        num_pages, page_size = cache.shape[0], cache.shape[1]
+    f = _fn("latent_prepare", "jv_latent_prepare",
+            [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+             c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+             c_void_p])
+    _check(f(row.data_ptr(), _code(row, "row"), row.stride(0), q_off, kv_off if writes else -1, _ptr(q_latent),
+             q_out.data_ptr(), q_out.stride(0), positions.data_ptr(), token_entry.data_ptr(), block_table.data_ptr(),
+             block_table.shape[1], _ptr(inv_freq), _ptr(norm_w) if writes else 0,
+             _code(norm_w, "norm") if writes else 0, float(eps), _ptr(cache) if writes else 0, n, heads, plain_dim,
+             rot_dim, latent_dim, page_size, num_pages, _status_ptr(row.device), _stream()), "latent_prepare")
+
+
+def gate_heads(o: torch.Tensor, gate: torch.Tensor | None) -> torch.Tensor:
+    """out[t, h*dv + d] = o[h, t, d] * sigmoid(gate[t, h*dv + d]) (no gate: the re-ordering alone);
+    `gate` may be a column slice of a wider tensor."""
+    _cuda(o, "o")
+    heads, n, dv = o.shape
+    g_stride = 0
+    if gate is not None:
+        _cuda(gate, "gate", o.dtype, contiguous=False)
+        if gate.shape != (n, heads * dv) or gate.stride(1) != 1:
+            raise KernelError("gate must be [n, heads * dv] with unit column stride")
+        g_stride = gate.stride(0)
+    out = torch.empty((n, heads * dv), dtype=o.dtype, device=o.device)
+    f = _fn("latent_prepare", "jv_gate_heads", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(o.data_ptr(), _ptr(gate), g_stride, out.data_ptr(), _code(o, "o"), n, heads, dv, _stream()), "gate_heads")
+    return out
+
+
+def bmm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One product per head: out[h] = a[h] @ w[h].T, a [heads, n, k] (any strides with unit inner stride),
+    w [heads, m, k] contiguous, out [heads, n, m] (made contiguous if not given; given, any strides with unit
+    inner stride).  float32 operands: the CUDA-core product of this package, k ascending (csrc/gemm_simt.cu);
+    bfloat16: the library's batched product (as the prompt products of this package are the library's)."""
+    _cuda(a, "a", contiguous=False); _cuda(w, "w", a.dtype)
+    heads, n, k = a.shape
+    m = w.shape[1]
+    if w.shape != (heads, m, k) or a.stride(2) != 1:
+        raise KernelError(f"batched product shapes {tuple(a.shape)} x {tuple(w.shape)}^T do not fit")
+    if a.dtype != torch.float32:
+        if out is None:
+            return torch.bmm(a, w.transpose(1, 2))
+        out.copy_(torch.bmm(a, w.transpose(1, 2)))
+        return out
+    if out is None:
+        out = torch.empty((heads, n, m), dtype=a.dtype, device=a.device)
+    _cuda(out, "out", a.dtype, contiguous=False)
+    if out.shape != (heads, n, m) or out.stride(2) != 1:
+        raise KernelError("out does not fit the batched product")
+    f = _fn("gemm_simt", "jv_gemm_tn_simt_batched", [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_longlong,
+                                                    c_void_p, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int,
+                                                    c_void_p])
+    _check(f(a.data_ptr(), _code(a, "a"), a.stride(1), a.stride(0), w.data_ptr(), _code(w, "w"), w.stride(1), w.stride(0),
+             out.data_ptr(), _code(out, "out"), out.stride(1), out.stride(0), n, m, k, heads, _stream()), "bmm_heads")
+    return out
+
+
+# ------------------------------------------------------------------- routed experts
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, groups: int, keep: int, renorm: bool):
+    """(ids [n, top] int32, weights [n, top] float32): router scores softmax(W x) in 32-bit, group-limited
+    choice of the `top` largest (csrc/moe_route.cu)."""
+    _cuda(x, "x", contiguous=False); _cuda(w_router, "router weight")
+    n, width = x.shape
+    experts = w_router.shape[0]
+    if w_router.shape != (experts, width) or x.stride(1) != 1:
+        raise KernelError("router weight does not fit the rows")
+    ids = torch.empty((n, top), dtype=torch.int32, device=x.device)
+    weights = torch.empty((n, top), dtype=torch.float32, device=x.device)
+    f = _fn("moe_route", "jv_moe_route", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_int, c_int, c_void_p, c_void_p, c_void_p])
+    _check(f(x.data_ptr(), _code(x, "x"), x.stride(0), w_router.data_ptr(), _code(w_router, "router"), n, width,
+             experts, top, groups, keep, 1 if renorm else 0, ids.data_ptr(), weights.data_ptr(), _stream()), "moe_route")
+    return ids, weights
+
+
+def moe_align(ids: torch.Tensor, experts: int, tile: int):
+    """The (token, choice) pairs in the order of their experts, each expert's run padded to `tile` rows:
+    (sorted_token [max_tiles * tile] (-1: padding), pos_of [n, top], tile_expert [max_tiles] (-1: unused))."""
+    _cuda(ids, "ids", torch.int32)
+    n, top = ids.shape
+    pairs = n * top
+    max_tiles = -(-(pairs + experts * (tile - 1)) // tile)
+    sorted_token = torch.empty(max_tiles * tile, dtype=torch.int32, device=ids.device)
+    pos_of = torch.empty((n, top), dtype=torch.int32, device=ids.device)
+    tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=ids.device)
+    f = _fn("moe_route", "jv_moe_align", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_void_p])
+    _check(f(ids.data_ptr(), pairs, top, experts, tile, max_tiles, sorted_token.data_ptr(), pos_of.data_ptr(),
+             tile_expert.data_ptr(), _status_ptr(ids.device), _stream()), "moe_align")
+    return sorted_token, pos_of, tile_expert
+
+
+MOE_ACTS = {None: 0, "gelu": 1}
+
+
+def moe_gemm_simt_tile() -> int:
+    f = _build.load("moe_gemm_simt").jv_moe_gemm_simt_tile
+    f.argtypes, f.restype = [], c_int
+    return int(f())
+
+
+def moe_gemm_simt(a: torch.Tensor, gather: torch.Tensor | None, w: torch.Tensor, tile_expert: torch.Tensor,
+                  out_dtype: torch.dtype, act: str | None = None) -> torch.Tensor:
+    """Grouped product on CUDA cores (csrc/moe_gemm_simt.cu): row pos of the result, in a tile of expert e, is
+    act(a[gather[pos]] @ w[e].T) (gather None: a[pos]); w [experts, N, K]; rows of padding are left unwritten."""
+    _cuda(a, "a"); _cuda(w, "w"); _cuda(tile_expert, "tile_expert", torch.int32)
+    tile = moe_gemm_simt_tile()
+    max_tiles = tile_expert.numel()
+    experts, n_out, k = w.shape
+    if a.shape[1] != k:
+        raise KernelError("grouped product: inner sizes differ")
+    if gather is not None:
+        _cuda(gather, "gather", torch.int32)
+        if gather.numel() != max_tiles * tile:
+            raise KernelError("gather does not fit the tiles")
+    elif a.shape[0] != max_tiles * tile:
+        raise KernelError("rows do not fit the tiles")
+    out = torch.empty((max_tiles * tile, n_out), dtype=out_dtype, device=a.device)
+    f = _fn("moe_gemm_simt", "jv_moe_gemm_simt", [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_longlong, c_int,
+                                                  c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                                  c_void_p])
+    _check(f(a.data_ptr(), _code(a, "a"), a.stride(0), _ptr(gather), a.shape[0], w.data_ptr(), _code(w, "w"), w.stride(0),
+             w.stride(1), tile_expert.data_ptr(), max_tiles, out.data_ptr(), _code(out, "out"), out.stride(0), n_out, k,
+             MOE_ACTS[act], _status_ptr(a.device), _stream()), "moe_gemm_simt")
+    return out
+
+
+# ---------------------------------------------------------------- per-layer token input
+def token_gate(z: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, offset: int) -> torch.Tensor:
+    """g[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], offset + j] (csrc/token_input.cu)."""
+    _cuda(z, "z"); _cuda(tokens, "tokens", torch.int32); _cuda(table, "table")
+    n, dim = z.shape
+    vocab, width = table.shape
+    if offset < 0 or offset + dim > width or tokens.numel() != n:
+        raise KernelError("token table does not fit")
+    g = torch.empty_like(z)
+    f = _fn("token_input", "jv_token_gate", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                             c_int, c_int, c_void_p, c_void_p])
+    _check(f(z.data_ptr(), _code(z, "z"), tokens.data_ptr(), table.data_ptr(), _code(table, "table"), width, offset,
+             vocab, g.data_ptr(), n, dim, _status_ptr(z.device), _stream()), "token_gate")
+    return g
 
 
 # ------------------------------------------------------------------------- sampling

@@ -38,6 +38,7 @@ class PagedKVNeed:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    shared_kv: bool = False       # the values are a leading part of the key rows: one tensor holds both
 
 
 @dataclass(frozen=True)
@@ -112,3 +113,6 @@ class StepContext:
     host_q_lens: list = field(default_factory=list)
     host_start_pos: list = field(default_factory=list)
     host_slots: list = field(default_factory=list)
+    # the stream rounded to the compute type, if the block that ran last left one for the next (a block that
+    # changes the stream without renewing it sets this to None)
+    stream_copy: Optional[torch.Tensor] = None

@@ -1,0 +1,166 @@
+"""Attention over a low-rank latent cache.
+
+A token leaves in the cache ONE row [c | r]: c = RMSNorm(first `latent_dim` outputs of the
+down-projection) and r = the rotated last `rot_dim` outputs, shared by all heads.  Head h's key
+is [W_uk_h c | r] and its value W_uv_h c.  Neither is ever formed: since
+
+    q_plain . (W_uk_h c) = (W_uk_h^T q_plain) . c        and        sum_j p_j W_uv_h c_j = W_uv_h (sum_j p_j c_j),
+
+the step multiplies the plain part of every query head by W_uk_h^T, runs attention with ONE
+key/value head whose key row is the cache row and whose value is the row's first
+`latent_dim` elements, and multiplies each head's result by W_uv_h:
+
+    row   = x @ [W_q; W_dkv; W_g]^T                       one product over the packed matrix
+    q_lat = q_plain_h @ W_uk_h      per head              ops.bmm_heads
+    cache row, q = [q_lat | rot(q_rot)]                   csrc/latent_prepare.cu (32-bit norm, angles, cos, sin)
+    o_lat = softmax(q k^T * scale + causal mask) c        the paged attention kernels, keys and values one tensor
+    o     = (o_lat_h @ W_uv_h^T) * sigmoid(gate)          ops.bmm_heads, ops.gate_heads
+    y     = o @ W_o^T
+
+A layer that reads another layer's cache has no down-projection and writes nothing.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import PagedKVNeed, Part, TensorSpec
+from .registry import POSITIONS, build, register_mixer
+
+
+class LatentAttention(Part):
+    kernels = ("latent_prepare", "attn_simt", "gemm_simt")
+
+    def __init__(self, spec, prefix, ctx):
+        self.spec, self.ctx = spec, ctx
+        self.prefix = f"{prefix}.{spec.prefix}" if spec.prefix else prefix
+        self.h, self.dp, self.dr = spec.num_heads, spec.plain_dim, spec.rot_dim
+        self.dv, self.dc = spec.value_dim, spec.latent_dim
+        self.dk = self.dc + self.dr                     # a cache row, and a query head as the attention kernel sees it
+        self.position = build(POSITIONS, "position encoding", spec.position, self.prefix, ctx) \
+            if spec.position is not None else None
+        if self.position is not None and self.position.dim != self.dr:
+            raise ValueError("the rotated part of a head is rotated whole: the rotation's size must equal rot_dim")
+        if self.dr % 2:
+            raise ValueError("rot_dim must be even")
+        self.writes_cache = True          # set False by the model for a layer that reads another's cache
+        # bfloat16 with a row size the tensor-core kernels are built for; else the CUDA-core kernel
+        self.use_mma = ops.attn_mma_supports(ctx.dtype, self.dk)
+        if self.use_mma:
+            self.kernels = ("latent_prepare", "attn_mma", "gemm_simt", "linear_skinny")
+            if self.dk == 128:
+                self.kernels += ("attn_tcgen05", "attn_decode_tcgen05")
+        self.w_in = self.w_uk = self.w_uv = self.w_o = self.latent_norm = None
+
+    # -------------------------------------------------------------------- weights
+    def _names(self):
+        keys = ("q", "dkv", "dkv_norm", "uk", "uv", "g", "o")
+        return {k: f"{self.prefix}.{n}" for k, n in zip(keys, self.spec.names)}
+
+    def tensor_specs(self):
+        n, s = self._names(), self.spec
+        specs = {n["q"]: TensorSpec((self.h * (self.dp + self.dr), s.hidden_size)),
+                 n["uk"]: TensorSpec((self.h * self.dp, self.dc)),
+                 n["uv"]: TensorSpec((self.h * self.dv, self.dc)),
+                 n["o"]: TensorSpec((s.hidden_size, self.h * self.dv))}
+        if s.output_gate:
+            specs[n["g"]] = TensorSpec((self.h * self.dv, s.hidden_size))
+        if self.writes_cache:
+            specs[n["dkv"]] = TensorSpec((self.dc + self.dr, s.hidden_size))
+            specs[n["dkv_norm"]] = TensorSpec((self.dc,), kind="vector", init="ones_normal")
+        return specs
+
+    def bind(self, tensors):
+        n = self._names()
+        mats = [tensors[n["q"]]]
+        self.kv_off = self.g_off = -1
+        rows = mats[0].shape[0]
+        if self.writes_cache:
+            self.kv_off = rows
+            mats.append(tensors[n["dkv"]])
+            rows += mats[-1].shape[0]
+            self.latent_norm = tensors[n["dkv_norm"]].contiguous()
+        if self.spec.output_gate:
+            self.g_off = rows
+            mats.append(tensors[n["g"]])
+        mats = [self.compute_weight(m, self.ctx) for m in mats]
+        if len({m.dtype for m in mats}) > 1:
+            mats = [m.to(torch.float32) for m in mats]
+        self.w_in = torch.cat(mats, dim=0).contiguous()
+        # per head: W_uk_h^T [latent_dim, plain_dim] (the product is x @ W^T), W_uv_h [value_dim, latent_dim]
+        uk = self.compute_weight(tensors[n["uk"]], self.ctx)
+        self.w_uk = uk.reshape(self.h, self.dp, self.dc).transpose(1, 2).contiguous()
+        self.w_uv = self.compute_weight(tensors[n["uv"]], self.ctx).reshape(self.h, self.dv, self.dc).contiguous()
+        self.w_o = self.compute_weight(tensors[n["o"]], self.ctx).contiguous()
+
+    # ---------------------------------------------------------------------- cache
+    def cache_need(self):
+        return PagedKVNeed(1, self.dk, None, shared_kv=True)
+
+    FOREVER = 1 << 30
+
+    def tile_classes(self, page_size: int):
+        small = (ops.attn_mma_tokens_per_tile if self.use_mma else ops.attn_simt_tokens_per_tile)(self.h, 1)
+        if ops.attn_tcgen05_supports(self.ctx.dtype, self.dk, self.h, 1, page_size, 0):
+            big = ops.attn_tcgen05_tokens_per_tile(self.h, 1)
+            return [(small, 2, big), (big, big, self.FOREVER)]
+        return [(small, 2, self.FOREVER)]
+
+    # ----------------------------------------------------------------------- step
+    def forward(self, x, step, cache):
+        dt, n, H = self.ctx.dtype, step.n_tokens, self.h
+        row = ops.linear(x, self.w_in, dt)
+        table = step.block_tables[cache.group]
+        writes = self.writes_cache and cache.writes
+        wide = row.dtype != torch.float32 and self.w_uk.dtype == torch.float32    # 32-bit-stored weights in 16-bit mode
+        q_plain = row[:, :H * (self.dp + self.dr)].view(n, H, self.dp + self.dr)[:, :, :self.dp].transpose(0, 1)
+        q = torch.empty((n, H * self.dk), dtype=dt, device=x.device)
+        if dt == torch.float32:
+            # the batched product writes the latent part of every query head in place
+            ops.bmm_heads(q_plain, self.w_uk, out=q.view(n, H, self.dk)[:, :, :self.dc].transpose(0, 1))
+            q_lat = None
+        else:
+            q_lat = ops.bmm_heads(q_plain, self.w_uk.to(dt) if wide else self.w_uk)
+        ops.latent_prepare(row, 0, self.kv_off, q_lat, q, step.positions, step.token_entry, table,
+                           self.position.table() if self.position is not None else None,
+                           self.latent_norm, self.spec.latent_norm_eps, cache.k if writes else None,
+                           H, self.dp, self.dr, self.dc)
+        o_lat = self.attend(q, step, cache, table)                      # [n, H, >= latent_dim], the latent part leads
+        o = ops.bmm_heads(o_lat[:, :, :self.dc].transpose(0, 1), self.w_uv.to(dt) if wide else self.w_uv)
+        gate = row[:, self.g_off:self.g_off + H * self.dv] if self.g_off >= 0 else None
+        return ops.linear(ops.gate_heads(o, gate), self.w_o, dt, parts_ok=True)
+
+    def attend(self, q, step, cache, table):
+        """One key/value head: the cache row is the key, its leading latent part the value."""
+        n, H, dk = step.n_tokens, self.h, self.dk
+        common = (cache.k, cache.k, table, step.cu_seqlens, step.start_pos)
+        if self.use_mma:
+            # the tensor-core kernels take keys and values of one size: they return whole rows, the latent part leads
+            out = torch.empty((n, H * dk), dtype=q.dtype, device=q.device)
+            extra, per_head = {}, dk
+            kernel = ops.attn_mma
+        else:
+            out = torch.empty((n, H * self.dc), dtype=q.dtype, device=q.device)
+            extra, per_head = {"v_dim": self.dc}, self.dc
+            kernel = ops.attn_simt
+        for cls in self.tile_classes(cache.k.shape[1]):
+            work, n_work = step.tile_work[cls]
+            if not n_work:
+                continue
+            if cls[2] == self.FOREVER and cls[1] > 2:      # the class of whole 128-row tiles
+                ops.attn_tcgen05(q, q.stride(0), out, *common, work, n_work, H, 1, dk, self.spec.scale)
+            else:
+                kernel(q, q.stride(0), out, *common, work, n_work, H, 1, dk, 0, self.spec.scale, **extra)
+        dwork, n_dec = step.decode_work
+        if n_dec and self.use_mma and ops.attn_decode_tcgen05_supports(self.ctx.dtype, dk, H, 1, cache.k.shape[1], 0, n_dec):
+            ops.attn_decode_tcgen05(q, q.stride(0), out, *common, dwork, n_dec, H, 1, dk, self.spec.scale)
+        elif n_dec:
+            split = self.ctx.decode_split_size
+            n_splits = max(1, -(-step.max_seq_len // split))
+            kernel(q, q.stride(0), out, *common, dwork, n_dec, H, 1, dk, 0, self.spec.scale,
+                   split_size=split, n_splits=n_splits, **extra)
+        return out.view(n, H, per_head)
+
+
+register_mixer("latent_attention", LatentAttention)

@@ -64,6 +64,7 @@ class Model(Part):
         if self.ctx.dtype == torch.bfloat16:
             names.update(("linear_skinny", "linear_stream"))
         for layer in self.layers:
+            names.update(layer.kernels)
             for part in layer.parts():
                 names.update(part.kernels)
         return sorted(names)
@@ -96,6 +97,7 @@ class Model(Part):
         with ops.trace_range("embedding"):
             h = ops.embed_gather(self.embedding, step.token_ids)
         delta = None
+        step.stream_copy = None
         for k, i in enumerate(self.order):
             with ops.trace_range(self.place_names[k]):
                 h, delta = self.layers[i].forward(h, delta, step, caches[self.place_cache[k]])

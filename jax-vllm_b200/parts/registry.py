@@ -8,6 +8,7 @@ FEED_FORWARDS: dict = {}
 NORMS: dict = {}
 POSITIONS: dict = {}
 BLOCKS: dict = {}
+TOKEN_INPUTS: dict = {}
 
 
 def _register(table, kind, cls):
@@ -20,6 +21,7 @@ def register_feed_forward(kind, cls): return _register(FEED_FORWARDS, kind, cls)
 def register_norm(kind, cls): return _register(NORMS, kind, cls)
 def register_position(kind, cls): return _register(POSITIONS, kind, cls)
 def register_block(kind, cls): return _register(BLOCKS, kind, cls)
+def register_token_input(kind, cls): return _register(TOKEN_INPUTS, kind, cls)
 
 
 def build(table: dict, what: str, spec, prefix: str, ctx):

@@ -1,0 +1,64 @@
+"""A mixture of small feed-forward experts, each down(act(up(x))), no biases.
+
+    ids, w   = route(x)                 softmax scores in 32-bit, group-limited choice of the top_k (csrc/moe_route.cu)
+    order    = pairs sorted by expert   every expert's rows padded to a row tile (csrc/moe_route.cu, jv_moe_align)
+    a        = act(x[token] @ W_up_e^T) grouped product, rows gathered as they are read, activation in its epilogue
+    y        = a @ W_down_e^T           grouped product
+    out[t]   = sum_k w[t, k] * y[pos(t, k)]     added up in 32-bit, k ascending, by the reader of the result
+
+The result is handed on as an `ops.PickedRows` (rows of y, which to pick and with which weight): the norm that
+follows adds them up as it reads them.  The expert matrices are kept stacked, [experts, out, in].
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import Part, TensorSpec
+from .registry import register_feed_forward
+
+
+class RoutedExperts(Part):
+    kernels = ("moe_route", "moe_gemm_simt")
+
+    def __init__(self, spec, prefix, ctx):
+        if spec.activation != "gelu":
+            raise ValueError(f"routed experts: activation {spec.activation!r} is not built (gelu is)")
+        if spec.scoring != "softmax":
+            raise ValueError(f"routed experts: scoring {spec.scoring!r} is not built (softmax is)")
+        E, n, keep = spec.num_experts, spec.n_groups, spec.keep_groups
+        if E % n or not 1 <= keep <= n or not 1 <= spec.top_k <= keep * (E // n):
+            raise ValueError(f"routed experts: {E} experts, {n} groups, {keep} kept, top {spec.top_k} do not fit")
+        self.spec, self.ctx = spec, ctx
+        self.prefix = f"{prefix}.{spec.prefix}" if spec.prefix else prefix
+        self.w_router = self.w_up = self.w_down = None
+
+    def tensor_specs(self):
+        p, s = self.prefix, self.spec
+        out = {f"{p}.router": TensorSpec((s.num_experts, s.hidden_size))}
+        for e in range(s.num_experts):
+            out[f"{p}.e{e}.up"] = TensorSpec((s.expert_size, s.hidden_size))
+            out[f"{p}.e{e}.down"] = TensorSpec((s.hidden_size, s.expert_size))
+        return out
+
+    def bind(self, tensors):
+        p, s = self.prefix, self.spec
+        self.w_router = tensors[f"{p}.router"].contiguous()
+        ups = [self.compute_weight(tensors[f"{p}.e{e}.up"], self.ctx) for e in range(s.num_experts)]
+        downs = [self.compute_weight(tensors[f"{p}.e{e}.down"], self.ctx) for e in range(s.num_experts)]
+        if len({m.dtype for m in ups + downs}) > 1:
+            ups, downs = [m.float() for m in ups], [m.float() for m in downs]
+        self.w_up = torch.stack(ups).contiguous()
+        self.w_down = torch.stack(downs).contiguous()
+
+    def forward(self, x, step):
+        s, dt = self.spec, self.ctx.dtype
+        ids, weights = ops.moe_route(x, self.w_router, s.top_k, s.n_groups, s.keep_groups, s.renormalize)
+        sorted_token, pos_of, tile_expert = ops.moe_align(ids, s.num_experts, ops.moe_gemm_simt_tile())
+        act = ops.moe_gemm_simt(x, sorted_token, self.w_up, tile_expert, dt, act="gelu")
+        y = ops.moe_gemm_simt(act, None, self.w_down, tile_expert, dt)
+        return ops.PickedRows(y, pos_of, weights)
+
+
+register_feed_forward("routed_experts", RoutedExperts)

@@ -21,9 +21,12 @@ def register_architecture(name: str, config_cls: type) -> None:
 
 def read_architecture(config_json: dict, where: str = "config.json") -> str:
     archs = config_json.get("architectures") or []
-    if not archs:
-        raise ValueError(f"no 'architectures' field in {where}")
-    return archs[0]
+    if archs:
+        return archs[0]
+    name = config_json.get("architecture")          # some designs name themselves with one string
+    if isinstance(name, str) and name:
+        return name
+    raise ValueError(f"no 'architectures' field in {where}")
 
 
 def config_from_dict(config_json: dict, where: str = "config.json"):
@@ -48,6 +51,9 @@ def _register_builtin() -> None:
     from .models.qwen3 import ARCHITECTURE, Qwen3Config
 
     register_architecture(ARCHITECTURE, Qwen3Config)
+    from .models.guronex import ARCHITECTURE as GURONEX, GuronexConfig
+
+    register_architecture(GURONEX, GuronexConfig)
 
 
 _register_builtin()

@@ -1,0 +1,177 @@
+"""Plain, slow, whole-sequence implementation of the Guronex design (on the CPU, float64 or
+float32): the oracle that the engine is compared with.
+
+No cache, no batching, no kernels: one function per mechanism, each written from the
+design's equations.  It shares no code with the product package: it reads config.json
+keys and safetensors names itself.
+
+The design, in this file's notation (h: a layer's input, [tokens, width]; m: the residual
+multiplier; rms(y) = y / sqrt(mean(y^2) + eps)):
+
+    x0          = embed[token]
+    x          <- x + m * rms(mixer(x)) * norm1
+    x          <- x + m * rms(ff(x)) * norm2                (if the layer has a feed-forward)
+    x          <- x + m * rms(side(x, token)) * side.norm   (if the model has per-layer token inputs)
+    logits      = head (rms(x) * final.norm)
+
+mixer = latent attention: queries per head [dim | rot_dim]; keys are made from a latent
+c = rms(first kv_rank rows of W_dkv h) * dkv.norm and one rotated part of rot_dim shared by all
+heads; key_h = [W_uk_h c | rot(k_r)], value_h = W_uv_h c; causal softmax; heads gated by
+sigmoid(W_g h); W_o.  A layer with `kv_from` = j takes c and rot(k_r) from layer j.
+
+ff = routed experts: s = softmax(W_router h) over all experts; experts in `count` groups of
+neighbours; a group scores as its best expert; only experts of the `keep` best groups may be
+chosen; the `top` best of those are chosen; out = sum s_e * W_down_e gelu(W_up_e h).
+"""
+
+from __future__ import annotations
+
+import json
+import math
+from pathlib import Path
+
+import torch
+
+
+def read_config(folder) -> dict:
+    return json.loads((Path(folder) / "config.json").read_text())
+
+
+def read_weights(folder, dtype=torch.float64) -> dict:
+    from safetensors import safe_open
+
+    out = {}
+    for shard in sorted(Path(folder).glob("*.safetensors")):
+        with safe_open(str(shard), framework="pt") as f:
+            for key in f.keys():
+                t = f.get_tensor(key)
+                out[key] = t.to(dtype) if t.is_floating_point() else t
+    return out
+
+
+# ----------------------------------------------------------------------- small parts
+def unit_rms(y: torch.Tensor, eps: float) -> torch.Tensor:
+    """y divided by its root mean square, eps inside the root."""
+    return y / torch.sqrt((y * y).mean(dim=-1, keepdim=True) + eps)
+
+
+def rms_norm(y, weight, eps):
+    return unit_rms(y, eps) * weight
+
+
+def gelu_tanh(z):
+    return 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+
+
+def gelu_erf(z):
+    return 0.5 * z * (1.0 + torch.erf(z / math.sqrt(2.0)))
+
+
+def rotate(u: torch.Tensor, positions: torch.Tensor, base: float) -> torch.Tensor:
+    """u [..., tokens, dims]: element i is paired with i + dims/2; the pair (a, b) at position p
+    becomes (a cos t - b sin t, b cos t + a sin t), t = p * base^(-2i/dims)."""
+    dims = u.shape[-1]
+    half = dims // 2
+    i = torch.arange(half, dtype=torch.float64)
+    freq = base ** (-2.0 * i / dims)
+    ang = positions.to(torch.float64)[:, None] * freq[None, :]
+    cos, sin = torch.cos(ang).to(u.dtype), torch.sin(ang).to(u.dtype)
+    a, b = u[..., :half], u[..., half:]
+    return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
+
+
+# ------------------------------------------------------------------ latent attention
+def latent_and_rotated_key(h, w, prefix, mx, eps, positions):
+    """What a layer with a W_dkv of its own leaves for itself and for the layers that read it:
+    c [tokens, kv_rank] and the rotated key part [tokens, rot_dim]."""
+    r = mx["kv_rank"]
+    d = h @ w[f"{prefix}.dkv"].T
+    c = rms_norm(d[:, :r], w[f"{prefix}.dkv.norm"], eps)
+    kr = rotate(d[:, r:], positions, mx["rot"]["base"])
+    return c, kr
+
+
+def latent_attention(h, w, prefix, mx, eps, positions, shared):
+    """`shared` = (c, rotated key part) of the layer this one reads, or None."""
+    T = h.shape[0]
+    H, dn, dr, dv = mx["heads"], mx["dim"], mx["rot_dim"], mx["vdim"]
+    assert mx["rot"]["dims"] == dr
+    c, kr = shared if shared is not None else latent_and_rotated_key(h, w, prefix, mx, eps, positions)
+    q = (h @ w[f"{prefix}.q"].T).reshape(T, H, dn + dr)
+    qn = q[:, :, :dn]
+    qr = rotate(q[:, :, dn:].transpose(0, 1), positions, mx["rot"]["base"]).transpose(0, 1)
+    kn = (c @ w[f"{prefix}.uk"].T).reshape(T, H, dn)
+    v = (c @ w[f"{prefix}.uv"].T).reshape(T, H, dv)
+    scores = (torch.einsum("thd,shd->hts", qn, kn) + torch.einsum("thd,sd->hts", qr, kr)) * mx["scale"]
+    visible = torch.arange(T)[None, :] <= torch.arange(T)[:, None]          # [query, key]
+    scores = scores.masked_fill(~visible[None], float("-inf"))
+    p = torch.softmax(scores, dim=-1)
+    o = torch.einsum("hts,shd->thd", p, v).reshape(T, H * dv)
+    o = o * torch.sigmoid(h @ w[f"{prefix}.g"].T)
+    return o @ w[f"{prefix}.o"].T, (c, kr)
+
+
+# -------------------------------------------------------------------- routed experts
+def route(h, w_router, rt):
+    """(chosen [tokens, top] expert indices, their weights): softmax over all experts, the best `keep`
+    groups by their best expert, the `top` best experts inside those; weights are the scores as they are."""
+    E, top = rt["experts"], rt["top"]
+    s = torch.softmax((h @ w_router.T).to(torch.float64), dim=-1)
+    allowed = torch.ones_like(s, dtype=torch.bool)
+    groups = rt.get("groups")
+    if groups is not None:
+        n, keep = groups["count"], groups["keep"]
+        best = s.reshape(-1, n, E // n).max(dim=-1).values                   # [tokens, groups]
+        kept = best.topk(keep, dim=-1).indices
+        gmask = torch.zeros_like(best, dtype=torch.bool).scatter_(1, kept, True)
+        allowed = gmask[:, :, None].expand(-1, n, E // n).reshape(-1, E)
+    chosen = s.masked_fill(~allowed, -1.0).topk(top, dim=-1).indices
+    return chosen, s.gather(1, chosen).to(h.dtype)
+
+
+def routed_experts(h, w, prefix, ml):
+    chosen, weight = route(h, w[f"{prefix}.router"], ml["router"])
+    out = torch.zeros_like(h)
+    for t in range(h.shape[0]):
+        for e, g in zip(chosen[t].tolist(), weight[t]):
+            a = gelu_erf(h[t] @ w[f"{prefix}.e{e}.up"].T)
+            out[t] += g * (a @ w[f"{prefix}.e{e}.down"].T)
+    return out
+
+
+# ------------------------------------------------------------- per-layer token input
+def token_side(x, tokens, w, layer, i, dim, eps):
+    e = w["side.embed"][tokens][:, i * dim:(i + 1) * dim]
+    g = gelu_tanh(x @ w[f"{layer}.side.gate"].T) * e
+    return rms_norm(g @ w[f"{layer}.side.proj"].T, w[f"{layer}.side.norm"], eps)
+
+
+# -------------------------------------------------------------------------- the model
+def forward(cfg: dict, w: dict, tokens, return_layers: bool = False):
+    """Logits [tokens, vocab] for one whole sequence (and the stream after every layer)."""
+    tokens = torch.as_tensor(tokens, dtype=torch.long)
+    positions = torch.arange(len(tokens))
+    eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
+    side = cfg.get("token_side")
+    x = w["embed"][tokens]
+    kept = {}
+    after = []
+    for i, layer in enumerate(cfg["layers"]):
+        p = f"l{i}"
+        if layer["type"] != "latent_attention":
+            raise ValueError(f"layer {i}: mixer {layer['type']!r}")
+        mx = layer["mixer"]
+        src = mx.get("kv_from")
+        y, mine = latent_attention(x, w, f"{p}.mix", mx, eps, positions, kept[src] if src is not None else None)
+        if src is None:
+            kept[i] = mine
+        x = x + m * rms_norm(y, w[f"{p}.norm1"], eps)
+        if layer.get("mlp") is not None:
+            if layer["mlp"]["kind"] != "moe":
+                raise ValueError(f"layer {i}: feed-forward {layer['mlp']['kind']!r}")
+            x = x + m * rms_norm(routed_experts(x, w, f"{p}.mlp", layer["mlp"]), w[f"{p}.norm2"], eps)
+        if side is not None:
+            x = x + m * token_side(x, tokens, w, p, i, side["dim"], eps)
+        after.append(x)
+    logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
+    return (logits, torch.stack(after)) if return_layers else logits
