@@ -29,7 +29,7 @@ constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTE
 constexpr int TMEM_COLS = 512;
 constexpr int THREADS = 192;
 
-enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2 };
+enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_GELU = 3 };
 
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
@@ -82,7 +82,9 @@ struct Shared {
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap a_map,
                                                                   const __grid_constant__ CUtensorMap b_map, void* C,
-                                                                  int ldc, int M, int N, int K, int* status) {
+                                                                  int ldc, int M, int N, int K, int* status,
+                                                                  const int* __restrict__ tile_expert,
+                                                                  int expert_rows) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Shared* sh = reinterpret_cast<Shared*>(tiles + STAGES * STAGE_BYTES);
@@ -115,12 +117,20 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        // grouped: the row tile belongs to one expert, whose rows of B start at expert * expert_rows; a row tile
+        // without an expert is skipped (by all three roles alike)
+        int b0 = n0;
+        if (tile_expert != nullptr) {
+          const int e = tile_expert[tile % tiles_m];
+          if (e < 0) continue;
+          b0 = e * expert_rows + n0;
+        }
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait(&sh->empty[s], phase ^ 1)) { ok = false; break; }
           sh->armed[s] = phase;
           mbar_expect_tx(&sh->full[s], STAGE_BYTES);
           tma_load_2d(tiles + s * STAGE_BYTES, &a_map, kb * BK, m0, &sh->full[s]);
-          tma_load_2d(tiles + s * STAGE_BYTES + A_BYTES, &b_map, kb * BK, n0, &sh->full[s]);
+          tma_load_2d(tiles + s * STAGE_BYTES + A_BYTES, &b_map, kb * BK, b0, &sh->full[s]);
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
       }
@@ -131,8 +141,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
     if (lane == 0) {
       int s = 0, phase = 0, it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        if (tile_expert != nullptr && tile_expert[tile % tiles_m] < 0) continue;
         const int acc = it & 1, acc_phase = (it >> 1) & 1;
+        ++it;
         if (!mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1)) { ok = false; break; }
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         const uint32_t tmem_d = tmem_base + acc * BN;
@@ -156,8 +168,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
     const int quad = warp & 3;                     // the 32 TMEM lanes this warp may read
     int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+      if (tile_expert != nullptr && tile_expert[tile % tiles_m] < 0) continue;
       const int acc = it & 1, acc_phase = (it >> 1) & 1;
+      ++it;
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
       if (!mbar_wait(&sh->acc_full[acc], acc_phase)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
@@ -196,6 +210,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
           float v[32];
           tmem_ld32(taddr + c * 32, v);
           const int col = n0 + c * 32;
+          if (EPI == EPI_GELU) {           // the exact gelu, 0.5 z (1 + erf(z / sqrt 2))
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = 0.5f * v[e] * (1.f + erff(v[e] * 0.70710678118654752f));
+          }
           if (row < M && col < N) {
             if (EPI == EPI_F32) {
               float* dst = reinterpret_cast<float*>(C) + (size_t)row * ldc + col;
@@ -274,7 +292,7 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int b
 
 template <int EPI>
 int launch(const CUtensorMap& a, const CUtensorMap& b, void* C, int ldc, int M, int N, int K, int* status,
-           cudaStream_t stream) {
+           cudaStream_t stream, const int* tile_expert = nullptr, int expert_rows = 0) {
   constexpr size_t smem = STAGES * STAGE_BYTES + sizeof(Shared) + 1024;
   static bool ready[JV_MAX_DEVICES];
   static int sm_count[JV_MAX_DEVICES];
@@ -292,7 +310,7 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, void* C, int ldc, int M, 
   const int sms = sm_count[dev];
   const int n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int blocks = n_tiles < sms ? n_tiles : sms;
-  gemm_tcgen05_kernel<EPI><<<blocks, THREADS, smem, stream>>>(a, b, C, ldc, M, N, K, status);
+  gemm_tcgen05_kernel<EPI><<<blocks, THREADS, smem, stream>>>(a, b, C, ldc, M, N, K, status, tile_expert, expert_rows);
   return jv_check_launch();
 }
 }  // namespace
@@ -312,6 +330,28 @@ JV_EXPORT int jv_gemm_tcgen05(const void* A, int lda, const void* B, int ldb, vo
     case EPI_BF16: return launch<EPI_BF16>(a_map, b_map, C, ldc, M, N, K, status, stream);
     case EPI_F32: return launch<EPI_F32>(a_map, b_map, C, ldc, M, N, K, status, stream);
     case EPI_SWIGLU: return launch<EPI_SWIGLU>(a_map, b_map, C, ldc, M, N, K, status, stream);
+  }
+  return JV_ERR_UNSUPPORTED;
+}
+
+JV_EXPORT int jv_moe_gemm_tcgen05_tile() { return BM; }
+
+// The grouped product of a mixture of experts: C[pos, :] = act(A[pos, :] * B[expert(pos)]^T), rows in tiles of 128
+// of one expert each (tile_expert[tile], -1: skipped).  A: [max_tiles * 128, K] bfloat16 rows of lda (rows of
+// padding may hold anything: a row of C depends on its own row of A only); B: [experts, N, K] bfloat16, contiguous
+// experts, rows of ldb; C: [max_tiles * 128, N] bfloat16 rows of ldc; epilogue 0: none, 3: the exact gelu.
+// A column tile that reaches beyond N reads the next expert's rows (or zeros); its columns beyond N are not written.
+JV_EXPORT int jv_moe_gemm_tcgen05(const void* A, int lda, const void* B, int ldb, int experts, const int* tile_expert,
+                                  int max_tiles, void* C, int ldc, int N, int K, int epilogue, int* status,
+                                  cudaStream_t stream) {
+  if (max_tiles == 0 || N == 0) return JV_OK;
+  if (K < 8 || (K % 8) || (lda % 8) || (ldb % 8) || ((uintptr_t)A % 16) || ((uintptr_t)B % 16)) return JV_ERR_UNSUPPORTED;
+  const int M = max_tiles * BM;
+  CUtensorMap a_map, b_map;
+  if (!make_map(&a_map, A, M, K, lda, BM) || !make_map(&b_map, B, experts * N, K, ldb, BN)) return JV_ERR_UNSUPPORTED;
+  switch (epilogue) {
+    case EPI_BF16: return launch<EPI_BF16>(a_map, b_map, C, ldc, M, N, K, status, stream, tile_expert, N);
+    case EPI_GELU: return launch<EPI_GELU>(a_map, b_map, C, ldc, M, N, K, status, stream, tile_expert, N);
   }
   return JV_ERR_UNSUPPORTED;
 }

@@ -134,7 +134,35 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
     pos_of[i] = pos;
   }
 }
+
+// out[pos_of[i], :] = x[i / top, :] for every (token, choice) pair i: the rows in the order of their experts.
+template <typename T>
+__global__ void moe_gather_rows_kernel(const T* __restrict__ x, int x_stride, const int* __restrict__ pos_of, int top,
+                                       T* __restrict__ out, int out_rows, int width) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x;
+  const int pos = pos_of[i];
+  if (pos < 0 || pos >= out_rows) return;
+  const T* src = x + (size_t)(i / top) * x_stride;
+  T* dst = out + (size_t)pos * width;
+  if (sizeof(T) == 2 && width % 8 == 0 && x_stride % 8 == 0) {
+    for (int c = threadIdx.x; c < width / 8; c += blockDim.x)
+      reinterpret_cast<uint4*>(dst)[c] = reinterpret_cast<const uint4*>(src)[c];
+  } else {
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
+  }
+}
 }  // namespace
+
+// x: [n, width] rows of x_stride; pos_of: [pairs]; out: [out_rows, width] (rows that no pair names are left alone).
+JV_EXPORT int jv_moe_gather_rows(const void* x, int dtype, int x_stride, const int* pos_of, int pairs, int top, void* out,
+                                 int out_rows, int width, cudaStream_t stream) {
+  if (pairs == 0) return JV_OK;
+  JV_DISPATCH_DTYPE(dtype, T, return jv_launch(moe_gather_rows_kernel<T>, dim3(pairs), dim3(128), 0, stream, (const T*)x,
+                                               x_stride, pos_of, top, (T*)out, out_rows, width));
+  return JV_ERR_UNSUPPORTED;
+}
 
 // x: [n, width] rows of x_stride elements (dtype); w: [experts, width] (w_dtype); ids: [n, top] int32;
 // weights: [n, top] float.

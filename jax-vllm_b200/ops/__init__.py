@@ -709,7 +709,7 @@ def _stream_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
             and x.dtype == torch.bfloat16)
 
 
-GEMM_EPILOGUES = {"bf16": 0, "f32": 1, "swiglu": 2}
+GEMM_EPILOGUES = {"bf16": 0, "f32": 1, "swiglu": 2, "gelu": 3}
 
 
 def gemm_tcgen05(x: torch.Tensor, weight: torch.Tensor, epilogue: str = "bf16") -> torch.Tensor:
@@ -981,6 +981,47 @@ def moe_gemm_simt(a: torch.Tensor, gather: torch.Tensor | None, w: torch.Tensor,
     _check(f(a.data_ptr(), _code(a, "a"), a.stride(0), _ptr(gather), a.shape[0], w.data_ptr(), _code(w, "w"), w.stride(0),
              w.stride(1), tile_expert.data_ptr(), max_tiles, out.data_ptr(), _code(out, "out"), out.stride(0), n_out, k,
              MOE_ACTS[act], _status_ptr(a.device), _stream()), "moe_gemm_simt")
+    return out
+
+
+def moe_gather_rows(x: torch.Tensor, pos_of: torch.Tensor, out_rows: int) -> torch.Tensor:
+    """The rows of `x` [n, width] in the order of their experts: out[pos_of[t, k]] = x[t]; rows of padding are
+    left as they are (csrc/moe_route.cu)."""
+    _cuda(x, "x", contiguous=False); _cuda(pos_of, "pos_of", torch.int32)
+    n, width = x.shape
+    if pos_of.shape[0] != n or x.stride(1) != 1:
+        raise KernelError("pos_of does not fit the rows")
+    out = torch.empty((out_rows, width), dtype=x.dtype, device=x.device)
+    f = _fn("moe_route", "jv_moe_gather_rows", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                                                c_void_p])
+    _check(f(x.data_ptr(), _code(x, "x"), x.stride(0), pos_of.data_ptr(), pos_of.numel(), pos_of.shape[1], out.data_ptr(),
+             out_rows, width, _stream()), "moe_gather_rows")
+    return out
+
+
+MOE_TCGEN05_TILE = 128
+
+
+def moe_gemm_tcgen05_supports(dtype: torch.dtype, w: torch.Tensor) -> bool:
+    """Whether the grouped tcgen05 product takes these expert matrices [experts, N, K] (csrc/gemm_tcgen05.cu)."""
+    return (dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.dim() == 3 and w.is_contiguous()
+            and w.shape[2] % 8 == 0 and w.shape[2] >= 8 and w.data_ptr() % 16 == 0)
+
+
+def moe_gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, act: str | None = None) -> torch.Tensor:
+    """Grouped product on tcgen05 (csrc/gemm_tcgen05.cu): row pos of the result, in a 128-row tile of expert e, is
+    act(a[pos] @ w[e].T); a [max_tiles * 128, K] bfloat16 in the order of the experts, w [experts, N, K]."""
+    _cuda(a, "a", torch.bfloat16); _cuda(w, "w", torch.bfloat16); _cuda(tile_expert, "tile_expert", torch.int32)
+    max_tiles = tile_expert.numel()
+    experts, n_out, k = w.shape
+    if a.shape != (max_tiles * MOE_TCGEN05_TILE, k):
+        raise KernelError("grouped product: rows do not fit the tiles")
+    out = torch.empty((a.shape[0], n_out), dtype=torch.bfloat16, device=a.device)
+    f = _fn("gemm_tcgen05", "jv_moe_gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
+                                                    c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(1), experts, tile_expert.data_ptr(), max_tiles,
+             out.data_ptr(), out.stride(0), n_out, k, GEMM_EPILOGUES["gelu" if act == "gelu" else "bf16"],
+             _status_ptr(a.device), _stream()), "moe_gemm_tcgen05")
     return out
 
 

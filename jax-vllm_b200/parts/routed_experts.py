@@ -51,10 +51,27 @@ class RoutedExperts(Part):
             ups, downs = [m.float() for m in ups], [m.float() for m in downs]
         self.w_up = torch.stack(ups).contiguous()
         self.w_down = torch.stack(downs).contiguous()
+        if self._tensor_cores():
+            self.kernels = ("moe_route", "gemm_tcgen05")
+
+    # The grouped tcgen05 product works on 128-row tiles of 256 columns: it is taken for bfloat16 experts whose inner
+    # sizes it can address (multiples of 8) and whose matrices are at least this wide; smaller ones, and the 32-bit
+    # path, go to the CUDA-core product with its 32-row tiles.
+    TCGEN05_MIN_SIZE = 128
+
+    def _tensor_cores(self) -> bool:
+        s = self.spec
+        return (ops.moe_gemm_tcgen05_supports(self.ctx.dtype, self.w_up) and ops.moe_gemm_tcgen05_supports(self.ctx.dtype, self.w_down)
+                and min(s.expert_size, s.hidden_size) >= self.TCGEN05_MIN_SIZE)
 
     def forward(self, x, step):
         s, dt = self.spec, self.ctx.dtype
         ids, weights = ops.moe_route(x, self.w_router, s.top_k, s.n_groups, s.keep_groups, s.renormalize)
+        if self._tensor_cores():
+            _, pos_of, tile_expert = ops.moe_align(ids, s.num_experts, ops.MOE_TCGEN05_TILE)
+            rows = ops.moe_gather_rows(x, pos_of, tile_expert.numel() * ops.MOE_TCGEN05_TILE)
+            act = ops.moe_gemm_tcgen05(rows, self.w_up, tile_expert, act="gelu")
+            return ops.PickedRows(ops.moe_gemm_tcgen05(act, self.w_down, tile_expert), pos_of, weights)
         sorted_token, pos_of, tile_expert = ops.moe_align(ids, s.num_experts, ops.moe_gemm_simt_tile())
         act = ops.moe_gemm_simt(x, sorted_token, self.w_up, tile_expert, dt, act="gelu")
         y = ops.moe_gemm_simt(act, None, self.w_down, tile_expert, dt)

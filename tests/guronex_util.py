@@ -56,8 +56,11 @@ GC = config(320, 128, [layer(mixer(8, 32, 16, 48, 112), moe(16, 4, 48, (2, 1))),
 GD = config(150, 80, [layer(mixer(20, 8, 8, 8, 24), moe(40, 5, 16, (5, 2)))], eps=1e-5, mult=0.7, side=5)
 # a long cache row (384) with values of 320
 GE = config(128, 64, [layer(mixer(2, 32, 64, 32, 320), moe(4, 2, 32))], eps=1e-5, mult=0.4, side=4)
-CONFIGS = {"ga": GA, "gb": GB, "gc": GC, "gd": GD, "ge": GE}
-PAGE = {"ga": 16, "gb": 8, "gc": 16, "gd": 4, "ge": 32}
+# experts of 128 and more (the grouped tcgen05 product in bfloat16), one size no multiple of its tiles
+GF = config(256, 128, [layer(mixer(4, 16, 16, 32, 48), moe(8, 2, 128, (2, 1))),
+                       layer(mixer(4, 16, 16, 32, 48, kv_from=0), moe(8, 3, 136))], eps=1e-5, mult=0.5, side=8)
+CONFIGS = {"ga": GA, "gb": GB, "gc": GC, "gd": GD, "ge": GE, "gf": GF}
+PAGE = {"ga": 16, "gb": 8, "gc": 16, "gd": 4, "ge": 32, "gf": 16}
 
 
 def tensor_shapes(c: dict) -> dict:

@@ -129,8 +129,35 @@ def route(h, w_router, rt):
     return chosen, s.gather(1, chosen).to(h.dtype)
 
 
-def routed_experts(h, w, prefix, ml):
+def route_margin(h, w_router, rt):
+    """Per token, how far the choice is from going another way: the smallest difference of router logits
+    between something that was taken (the last chosen expert, the last kept group) and the best that was not.
+    A 16-bit computation may choose otherwise where this is small; such a token's result is then another."""
+    E, top = rt["experts"], rt["top"]
+    z = (h @ w_router.T).to(torch.float64)
+    chosen, _ = route(h, w_router, rt)
+    taken = torch.zeros_like(z, dtype=torch.bool).scatter_(1, chosen, True)
+    margin = torch.full((h.shape[0],), float("inf"), dtype=torch.float64)
+    allowed = torch.ones_like(taken)
+    groups = rt.get("groups")
+    if groups is not None and groups["keep"] < groups["count"]:
+        n, keep = groups["count"], groups["keep"]
+        best = z.reshape(-1, n, E // n).max(dim=-1).values.sort(dim=-1, descending=True).values
+        margin = best[:, keep - 1] - best[:, keep]
+        kept = z.reshape(-1, n, E // n).max(dim=-1).values >= best[:, keep - 1:keep]
+        allowed = kept[:, :, None].expand(-1, n, E // n).reshape(-1, E)
+    rest = z.masked_fill(taken | ~allowed, float("-inf")).max(dim=-1).values
+    last = z.masked_fill(~taken, float("inf")).min(dim=-1).values
+    return torch.minimum(margin, last - rest)
+
+
+def routed_experts(h, w, prefix, ml, forced=None):
+    """`forced` [tokens, top]: these experts are taken instead of the router's choice (their weights are still the
+    router's scores): for following a 16-bit computation whose choice went the other way at a close call."""
     chosen, weight = route(h, w[f"{prefix}.router"], ml["router"])
+    if forced is not None:
+        chosen = forced
+        weight = torch.softmax((h @ w[f"{prefix}.router"].T).to(torch.float64), dim=-1).gather(1, chosen).to(h.dtype)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, g in zip(chosen[t].tolist(), weight[t]):
@@ -147,8 +174,11 @@ def token_side(x, tokens, w, layer, i, dim, eps):
 
 
 # -------------------------------------------------------------------------- the model
-def forward(cfg: dict, w: dict, tokens, return_layers: bool = False):
-    """Logits [tokens, vocab] for one whole sequence (and the stream after every layer)."""
+def forward(cfg: dict, w: dict, tokens, return_layers: bool = False, margins: list | None = None,
+            forced: list | None = None, free: list | None = None):
+    """Logits [tokens, vocab] for one whole sequence (and the stream after every layer).  `margins`, if given,
+    receives one tensor per routed layer: every token's `route_margin` there; `free` the router's own choice
+    there; `forced` (one [tokens, top] tensor per routed layer) makes the layers take those experts."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(len(tokens))
     eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
@@ -156,6 +186,7 @@ def forward(cfg: dict, w: dict, tokens, return_layers: bool = False):
     x = w["embed"][tokens]
     kept = {}
     after = []
+    routed = 0
     for i, layer in enumerate(cfg["layers"]):
         p = f"l{i}"
         if layer["type"] != "latent_attention":
@@ -169,7 +200,13 @@ def forward(cfg: dict, w: dict, tokens, return_layers: bool = False):
         if layer.get("mlp") is not None:
             if layer["mlp"]["kind"] != "moe":
                 raise ValueError(f"layer {i}: feed-forward {layer['mlp']['kind']!r}")
-            x = x + m * rms_norm(routed_experts(x, w, f"{p}.mlp", layer["mlp"]), w[f"{p}.norm2"], eps)
+            if margins is not None:
+                margins.append(route_margin(x, w[f"{p}.mlp.router"], layer["mlp"]["router"]))
+            if free is not None:
+                free.append(route(x, w[f"{p}.mlp.router"], layer["mlp"]["router"])[0])
+            force = forced[routed] if forced is not None else None
+            routed += 1
+            x = x + m * rms_norm(routed_experts(x, w, f"{p}.mlp", layer["mlp"], force), w[f"{p}.norm2"], eps)
         if side is not None:
             x = x + m * token_side(x, tokens, w, p, i, side["dim"], eps)
         after.append(x)

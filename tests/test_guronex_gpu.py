@@ -17,13 +17,64 @@ import torch
 
 from tests.guronex_util import CONFIGS, PAGE, config, layer, make_weights, mixer, moe, write_folder
 from tests.plain import guronex_plain as gp
-from tests.test_replay_gpu import compare
+from tests.test_replay_gpu import limits
 from tests.util import portions, prefix_then_single, random_tokens, whole
 
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 LENGTHS = {"ga": [70, 45, 100, 33], "gb": [90, 38, 64, 51], "gc": [200, 70, 150, 40], "gd": [61, 40, 83, 35],
-           "ge": [80, 37, 50, 20]}
+           "ge": [80, 37, 50, 20], "gf": [150, 40, 90, 30]}
+
+
+CLOSE_CALL = 0.1       # a difference of router logits below which bfloat16 may choose another expert
+EXCUSED = 0.25         # share of the positions that may differ for that reason (where the choice cannot be followed)
+
+
+def oracle(c, w, tokens):
+    """(logits, positions whose routing is a close call in some layer)."""
+    margins = []
+    logits = gp.forward(c, w, tokens, margins=margins).to(torch.float32)
+    close = set()
+    for m in margins:
+        close.update(torch.nonzero(m < CLOSE_CALL).flatten().tolist())
+    return logits, close
+
+
+def compare(steps, out_dir, vocab, want, dtype, case=None, close=None, floor=None):
+    """Every written row against the oracle's; 32-bit holds every position.  In bfloat16 a token whose choice of
+    experts hangs on a small difference of router logits (`close`: request -> positions where the oracle finds
+    one) may choose otherwise, and what comes after it attends to the changed token: a position over the limit is
+    excused only if such a token stands at or before it, and no more than EXCUSED of all positions are.  `floor`
+    (request -> per position) is the rounding error of the plain implementation itself in 32-bit, where a case is
+    badly conditioned by design; the limit is at least 3 times it.  The largest |difference| that was held is
+    recorded under `case`."""
+    from tests.conftest import record_worst
+    from tests.util import collect
+    got = collect(steps, out_dir, vocab)
+    worst, lim_of_worst, excused, total = 0.0, 0.0, 0, 0
+    for rid, rows in got.items():
+        base = limits(dtype, want[rid])
+        first_close = min(close.get(rid) or [1 << 30]) if (close is not None and dtype != "float32") else 1 << 30
+        for pos, row in rows.items():
+            total += 1
+            lim = base if floor is None else max(base, 3.0 * float(floor[rid][pos]))
+            w = want[rid][pos]
+            diff = (torch.from_numpy(row.copy()) - w).abs().max().item()
+            if diff > lim and pos >= first_close:
+                excused += 1
+                continue
+            assert diff <= lim, f"{rid} position {pos}: |diff| {diff:.3e} > {lim:.3e}"
+            if diff >= worst:
+                worst, lim_of_worst = diff, lim
+            if dtype == "float32" and floor is None:
+                assert int(row.argmax()) == int(w.argmax())
+    assert excused <= EXCUSED * total, f"{excused} of {total} positions differ"
+    if case is not None:
+        record_worst(case, dtype, worst, lim_of_worst)
+    return got, worst
+
+
+W64: dict = {}         # configuration tag -> the stored weights as float64 (set by the fixture)
 
 
 def stored(weights: dict) -> dict:
@@ -37,11 +88,13 @@ def setup(request, tmp_path_factory):
     c = CONFIGS[tag]
     weights = make_weights(c, seed=5)
     folder = write_folder(tmp_path_factory.mktemp(f"guronex_{tag}"), c, weights)
-    w = stored(weights)
+    w = W64[tag] = stored(weights)
     seqs = {f"r{i}": random_tokens(n, c["vocab"], seed=20 + i) for i, n in enumerate(LENGTHS[tag])}
-    want = {rid: gp.forward(c, w, t).to(torch.float32) for rid, t in seqs.items()}
+    both = {rid: oracle(c, w, t) for rid, t in seqs.items()}
+    want = {rid: v[0] for rid, v in both.items()}
+    close = {rid: v[1] for rid, v in both.items()}
     assert all(v.abs().max() > 1.0 for v in want.values())     # logits of order one, not a flat model
-    return tag, folder, seqs, want
+    return tag, folder, seqs, (want, close)
 
 
 def replay(folder, tag, dtype, steps, out_dir, max_tokens, **switches):
@@ -53,8 +106,59 @@ def replay(folder, tag, dtype, steps, out_dir, max_tokens, **switches):
     return rep
 
 
+class Routes:
+    """Records which experts the engine chose, call by call (a context manager around a replay), and puts them
+    back together per request: {request: [one [tokens, top] tensor per routed layer]}."""
+
+    def __enter__(self):
+        from jax_vllm_b200 import ops
+        self.ops, self.orig, self.calls = ops, ops.moe_route, []
+
+        def recording(*a, **k):
+            ids, weights = self.orig(*a, **k)
+            self.calls.append(ids.cpu().long())
+            return ids, weights
+        ops.moe_route = recording
+        return self
+
+    def __exit__(self, *exc):
+        self.ops.moe_route = self.orig
+        return False
+
+    def per_request(self, steps, n_routed):
+        assert len(self.calls) == n_routed * len(steps)          # every step ran every routed layer once, eagerly
+        out = {}
+        for k, s in enumerate(steps):
+            at = 0
+            for e in s["entries"]:
+                n = len(e["tokens"])
+                for layer in range(n_routed):
+                    out.setdefault(e["id"], [[] for _ in range(n_routed)])[layer].append(self.calls[k * n_routed + layer][at:at + n])
+                at += n
+        return {rid: [torch.cat(parts) for parts in layers] for rid, layers in out.items()}
+
+
+def replay_bf16_following_the_engines_choice(folder, tag, c, w, seqs, steps, out_dir, max_tokens, case):
+    """bfloat16, every position held: the plain implementation is made to take the experts that the engine took,
+    and the engine may have taken others than the plain router only where the router logits nearly tie."""
+    with Routes() as routes:
+        rep = replay(folder, tag, "bfloat16", steps, out_dir, max_tokens)
+    n_routed = sum(1 for ly in c["layers"] if ly["mlp"] is not None)
+    taken = routes.per_request(steps, n_routed)
+    want = {}
+    for rid, forced in taken.items():
+        margins, free = [], []
+        want[rid] = gp.forward(c, w, seqs[rid][:forced[0].shape[0]] if forced else seqs[rid], margins=margins, forced=forced,
+                               free=free).to(torch.float32)
+        for layer in range(n_routed):
+            differs = (forced[layer].sort(dim=1).values != free[layer].sort(dim=1).values).any(dim=1)
+            assert (margins[layer][differs] < CLOSE_CALL).all(), f"{rid}: the engine chose other experts far from a tie"
+    compare(steps, out_dir, c["vocab"], want, "bfloat16", case=case)
+    return rep
+
+
 # ------------------------------------------------------------------ mechanisms alone
-@pytest.mark.parametrize("experts,top,groups,width", [(8, 2, (4, 2), 64), (40, 5, (5, 2), 80), (6, 1, (1, 1), 96),
+@pytest.mark.parametrize("experts,top,groups,width", [(8, 3, (4, 2), 64), (40, 5, (5, 2), 80), (6, 1, (1, 1), 96),
                                                       (12, 3, (3, 3), 50), (16, 4, None, 128), (64, 6, (8, 3), 256)])
 def test_router_alone(experts, top, groups, width):
     from jax_vllm_b200 import ops
@@ -70,35 +174,43 @@ def test_router_alone(experts, top, groups, width):
     assert ids.cpu().tolist() == chosen.tolist()                # largest first, as the oracle's topk gives them
     assert torch.allclose(wts.cpu().double(), weight, rtol=1e-5, atol=1e-7)
     assert not torch.allclose(wts.sum(dim=1).cpu(), torch.ones(70))          # the scores are not renormalised
-    if groups is not None and groups[1] < groups[0]:
+    if groups is not None and groups[1] < min(top, groups[0]):    # more groups could be hit than are kept
         free, _ = gp.route(x.double(), w.double(), {"experts": experts, "top": top})
         assert free.tolist() != chosen.tolist()                 # the groups do restrict the choice in this case
 
 
+@pytest.mark.parametrize("W,E,ff,top,tensor_cores", [(72, 10, 24, 3, False), (256, 10, 136, 3, True)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_routed_experts_alone(dtype):
-    """The part by itself: route, order by expert, two grouped products, weighted sum by the reader."""
+def test_routed_experts_alone(dtype, W, E, ff, top, tensor_cores):
+    """The part by itself: route, order by expert, two grouped products (on CUDA cores; in bfloat16 at sizes
+    from 128 on the tcgen05 product, also with an expert size that is no multiple of its tiles), weighted sum by
+    the reader."""
     from jax_vllm_b200.config.model_spec import RoutedExpertsSpec
     from jax_vllm_b200.parts import BuildContext
     from jax_vllm_b200.parts.routed_experts import RoutedExperts
-    W, E, ff, top = 72, 10, 24, 3
     g = torch.Generator().manual_seed(3)
-    tensors = {"f.router": torch.randn((E, W), generator=g) * 0.3}
+    tensors = {"b.f.router": torch.randn((E, W), generator=g) * 0.3}
     for e in range(E):
-        tensors[f"f.e{e}.up"] = torch.randn((ff, W), generator=g) / W ** 0.5
-        tensors[f"f.e{e}.down"] = torch.randn((W, ff), generator=g) / ff ** 0.5
+        tensors[f"b.f.e{e}.up"] = torch.randn((ff, W), generator=g) / W ** 0.5
+        tensors[f"b.f.e{e}.down"] = torch.randn((W, ff), generator=g) / ff ** 0.5
     tensors = {k: v.to(torch.bfloat16) for k, v in tensors.items()}
-    part = RoutedExperts(RoutedExpertsSpec(W, E, top, ff, n_groups=5, keep_groups=3, prefix="f"), "",
+    part = RoutedExperts(RoutedExpertsSpec(W, E, top, ff, n_groups=5, keep_groups=3, prefix="f"), "b",
                          BuildContext(dtype=dtype, device=torch.device("cuda")))
     assert set(part.tensor_specs()) == set(tensors)
     part.bind({k: v.cuda() for k, v in tensors.items()})
-    for n in (1, 5, 97):                                        # fewer rows than experts, and several tiles
+    assert part._tensor_cores() == (tensor_cores and dtype == torch.bfloat16)
+    ml = {"router": {"experts": E, "top": top, "groups": {"count": 5, "keep": 3}}}
+    w64 = {k: v.double() for k, v in tensors.items()}
+    for n in (1, 5, 97, 700):                                   # fewer rows than experts, and several tiles an expert
         x = torch.randn((n, W), generator=g).to(torch.bfloat16)
         got = part.forward(x.cuda().to(dtype), None).tensor().cpu().double()
-        ml = {"router": {"experts": E, "top": top, "groups": {"count": 5, "keep": 3}}}
-        want = gp.routed_experts(x.double(), {k: v.double() for k, v in tensors.items()}, "f", ml)
+        want = gp.routed_experts(x.double(), w64, "b.f", ml)
+        sure = gp.route_margin(x.double(), w64["b.f.router"], ml["router"]) > 1e-3
         lim = 1e-5 if dtype == torch.float32 else 3e-2
-        assert (got - want).abs().max() <= lim * max(1.0, want.abs().max().item())
+        assert sure.sum() > 0.9 * n
+        assert (got - want)[sure].abs().max() <= lim * max(1.0, want.abs().max().item())
+    from jax_vllm_b200 import ops
+    ops.check_status()
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -190,8 +302,12 @@ def test_each_request_alone_and_whole(setup, dtype, tmp_path):
     tag, folder, seqs, want = setup
     for rid, toks in seqs.items():
         steps = whole(rid, toks)
+        if dtype == "bfloat16":
+            replay_bf16_following_the_engines_choice(folder, tag, CONFIGS[tag], W64[tag], seqs, steps, tmp_path / rid, 128 * 3,
+                                                     f"guronex {tag}, whole")
+            continue
         replay(folder, tag, dtype, steps, tmp_path / rid, max_tokens=128 * 3)
-        compare(steps, tmp_path / rid, CONFIGS[tag]["vocab"], want, dtype, case=f"guronex {tag}, whole")
+        compare(steps, tmp_path / rid, CONFIGS[tag]["vocab"], want[0], dtype, case=f"guronex {tag}, whole", close=want[1])
 
 
 @pytest.mark.parametrize("graphs", [False, True])
@@ -200,9 +316,13 @@ def test_last_tokens_one_by_one(setup, dtype, graphs, tmp_path):
     """Prefill against token-by-token decoding, eagerly and from the captured graph."""
     tag, folder, seqs, want = setup
     steps = prefix_then_single("r0", seqs["r0"], tail=24)
+    if dtype == "bfloat16" and not graphs:
+        replay_bf16_following_the_engines_choice(folder, tag, CONFIGS[tag], W64[tag], seqs, steps, tmp_path, 256,
+                                                 f"guronex {tag}, decoding")
+        return
     rep = replay(folder, tag, dtype, steps, tmp_path, max_tokens=256, cuda_graphs=graphs)
     assert any(m["replayed_graph"] for m in rep.records) == graphs
-    compare(steps, tmp_path, CONFIGS[tag]["vocab"], want, dtype, case=f"guronex {tag}, decoding")
+    compare(steps, tmp_path, CONFIGS[tag]["vocab"], want[0], dtype, case=f"guronex {tag}, decoding", close=want[1])
 
 
 @pytest.mark.parametrize("sizes", [(2,), (7, 2, 13, 1, 1, 5), (33, 3, 64)])
@@ -210,8 +330,12 @@ def test_last_tokens_one_by_one(setup, dtype, graphs, tmp_path):
 def test_portions_of_changing_size(setup, dtype, sizes, tmp_path):
     tag, folder, seqs, want = setup
     steps = portions("r2", seqs["r2"], sizes)
+    if dtype == "bfloat16":
+        replay_bf16_following_the_engines_choice(folder, tag, CONFIGS[tag], W64[tag], seqs, steps, tmp_path, 256,
+                                                 f"guronex {tag}, portions {sizes}")
+        return
     replay(folder, tag, dtype, steps, tmp_path, max_tokens=256)
-    compare(steps, tmp_path, CONFIGS[tag]["vocab"], want, dtype, case=f"guronex {tag}, portions {sizes}")
+    compare(steps, tmp_path, CONFIGS[tag]["vocab"], want[0], dtype, case=f"guronex {tag}, portions {sizes}", close=want[1])
 
 
 def mixed_trace(seqs):
@@ -239,15 +363,19 @@ def test_unequal_requests_side_by_side_in_reused_pages(setup, dtype, tmp_path):
     steps = mixed_trace(seqs)
     P = PAGE[tag]
     live3 = sum(sorted(-(-len(s) // P) * P for s in seqs.values())[-3:])
-    rep = replay(folder, tag, dtype, steps, tmp_path, max_tokens=live3)
+    if dtype == "bfloat16":
+        rep = replay_bf16_following_the_engines_choice(folder, tag, CONFIGS[tag], W64[tag], seqs, steps, tmp_path, live3,
+                                                       f"guronex {tag}, side by side")
+    else:
+        rep = replay(folder, tag, dtype, steps, tmp_path, max_tokens=live3)
+        compare(steps, tmp_path, CONFIGS[tag]["vocab"], want[0], dtype, case=f"guronex {tag}, side by side", close=want[1])
     assert sum(m["pages_allocated"] for m in rep.records) > rep.cache.num_pages * len(rep.cache.groups)   # pages came back and went out again
-    compare(steps, tmp_path, CONFIGS[tag]["vocab"], want, dtype, case=f"guronex {tag}, side by side")
 
 
 def test_schedules_agree_with_each_other_in_32_bit(setup, tmp_path):
     """A position's logits do not depend on the cut, the batch or the pages beyond rounding."""
     from tests.util import collect
-    tag, folder, seqs, want = setup
+    tag, folder, seqs, _ = setup
     V = CONFIGS[tag]["vocab"]
     a = whole("r0", seqs["r0"])
     b = portions("r0", seqs["r0"], (5, 1, 2, 19))
@@ -311,10 +439,10 @@ def test_one_far_key_among_hundreds(far, dtype, tmp_path):
     target = torch.einsum("hdr,r->hd", uk, c1[0])                      # the plain key of token 1, per head
     x2 = w64["embed"][2]
     q = torch.zeros((2, 24, 64), dtype=torch.float64)
-    q[:, :16, :] = 0.5 * target[:, :, None] * x2[None, None, :] / (x2 @ x2)
+    q[:, :16, :] = 1.5 * target[:, :, None] * x2[None, None, :] / (x2 @ x2)
     w["l0.mix.q"] = q.reshape(48, 64).to(torch.float32)
     w64 = stored(w)
-    with_key = gp.forward(c, w64, tokens).to(torch.float32)
+    with_key = gp.forward(c, w64, tokens).to(torch.float32)          # no routed layer: nothing hangs on a close call
     without = list(tokens)
     without[far] = 4
     gone = gp.forward(c, w64, without).to(torch.float32)
@@ -334,10 +462,15 @@ def test_values_that_happen_to_be_one_or_equal(dtype, tmp_path):
                            config(64, 32, [layer(mixer(2, 16, 16, 16, 16), moe(4, 2, 32, (2, 1)))], mult=0.05, side=16))):
         w = make_weights(c, seed=13 + k)
         tokens = random_tokens(45, 64, seed=14)
-        want = {"r": gp.forward(c, stored(w), tokens).to(torch.float32)}
+        logits, close = oracle(c, stored(w), tokens)
+        # a token input of ONE column is normed to +-1 times its projection unless the column is tiny: there the
+        # 32-bit rounding of the gate shows.  What the plain implementation itself loses in 32-bit is the floor.
+        w32 = {name: v.to(torch.bfloat16).to(torch.float32) for name, v in w.items()}
+        floor = (gp.forward(c, w32, tokens).double() - gp.forward(c, stored(w), tokens)).abs().max(dim=1).values
         for sizes in (None, (2,)):
             steps, out = special(tmp_path / str(k), c, w, tokens, dtype, sizes=sizes, page=8)
-            compare(steps, out, 64, want, dtype, case="guronex sizes of one")
+            compare(steps, out, 64, {"r": logits}, dtype, case=f"guronex sizes of one ({k})", close={"r": close},
+                    floor={"r": floor} if dtype == "float32" else None)
 
 
 # ----------------------------------------------------------- generation, scheduler, entry point
