@@ -489,6 +489,147 @@ def workload(name: str, layers) -> int:
     return 0
 
 
+# ------------------------------------------------------------------ the Guronex design beside Qwen3
+# Layer sizes for `--design guronex`: each a Guronex layer (latent attention + routed experts + token input) and the
+# Qwen3 dense layer of equal width, equal number of heads and about equal feed-forward work per token
+# (3 * intermediate = 2 * top * expert size).  "lite": the width, experts and expert size of a 16B-class mixture
+# with a cache row of 128 (latent 96 + rotated 32), the size the tcgen05 attention kernels take; "mid": a wider
+# one; "row576": the cache row of published latent-attention models (latent 512 + rotated 64), which runs on the
+# CUDA-core attention kernel here.
+DESIGN_SIZES = {
+    "lite": dict(width=2048, heads=16, dim=64, rot=32, vdim=64, rank=96, experts=64, top=6, ff=1408, groups=(8, 4), side=64),
+    "mid": dict(width=4096, heads=32, dim=96, rot=32, vdim=128, rank=96, experts=32, top=4, ff=2048, groups=(4, 2), side=64),
+    "row576": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=512, experts=64, top=6, ff=1408, groups=(8, 4), side=64),
+}
+
+
+def design_configs(z, layers, vocab=32000):
+    mixer = {"heads": z["heads"], "dim": z["dim"], "rot_dim": z["rot"], "vdim": z["vdim"], "kv_rank": z["rank"],
+             "rot": {"base": 10000.0, "dims": z["rot"]}, "scale": (z["dim"] + z["rot"]) ** -0.5}
+    mlp = {"kind": "moe", "expert": {"ff": z["ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
+    guronex = {"architecture": "Guronex", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.3,
+               "token_side": {"dim": z["side"]},
+               "layers": [{"type": "latent_attention", "mixer": dict(mixer), "mlp": mlp} for _ in range(layers)]}
+    inter = -(-(2 * z["top"] * z["ff"] // 3) // 128) * 128
+    qwen = dict(QWEN3_8B, vocab_size=vocab, hidden_size=z["width"], intermediate_size=inter, num_hidden_layers=layers,
+                num_attention_heads=z["heads"], num_key_value_heads=max(1, z["heads"] // 4), head_dim=128)
+    return guronex, qwen
+
+
+def time_part(fn, reps, flush):
+    """Median device time (us) of `fn`, one launch sequence at a time, the L2 written over in between."""
+    import torch
+    for _ in range(3):
+        fn()
+    times = []
+    for _ in range(reps):
+        flush.add_(1)
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(); fn(); e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e) * 1e3)
+    return statistics.median(times)
+
+
+def design_parts(model, kind, z, inter, batch, tokens, reps, pk):
+    """The attention kernel alone, the whole mixer and the whole feed-forward of layer 0: one prompt of `tokens`
+    tokens, then one decode step of `batch` requests at CONTEXT tokens; each with its roofline (FLOPs over the
+    measured bf16 peak for the prompt, bytes over the measured copy bandwidth for the decode step)."""
+    import torch
+    from jax_vllm_b200 import make_driver
+    from jax_vllm_b200.engine import StepEntry
+    W, H = z["width"], z["heads"]
+    flush = torch.zeros(160 << 20, dtype=torch.int16, device="cuda")
+    out = {}
+    layer = model.layers[0]
+    for phase in ("prefill", "decode"):
+        if phase == "prefill":
+            driver = make_driver(model, max_num_seqs=1, max_model_len=tokens + 16, block_size=PAGE, prefix_cache=False,
+                                 max_tokens_per_step=tokens, cuda_graphs=False)
+            rc = driver.cache.admit("p")
+            driver.cache.grow(rc, tokens)
+            entries = [StepEntry(rc, [(i * 7919 + 13) % 1000 for i in range(tokens)], (tokens - 1,))]
+            n, pairs = tokens, tokens * (tokens + 1) // 2
+        else:
+            driver = make_driver(model, max_num_seqs=batch, max_model_len=CONTEXT + 64, block_size=PAGE, prefix_cache=False,
+                                 cuda_graphs=False)
+            rcs = fake_context(driver, batch, CONTEXT)
+            for rc in rcs:
+                driver.cache.grow(rc, rc.num_tokens + 1)
+            entries = [StepEntry(rc, [b], (0,)) for b, rc in enumerate(rcs)]
+            n, pairs = batch, batch * (CONTEXT + 1)
+        step = driver.runner.builder.build(entries)
+        cache = driver.runner.layer_caches[0]
+        table = step.block_tables[cache.group]
+        x = (torch.randn((n, W), device="cuda") * 0.5).to(torch.bfloat16)
+        mixer, ff = layer.mixer, layer.feed_forward
+        if kind == "guronex":
+            dk, dc = z["rank"] + z["rot"], z["rank"]
+            q = torch.randn((n, H * dk), device="cuda").to(torch.bfloat16)
+            attn = lambda: mixer.attend(q, step, cache, table)
+            attn_flops, attn_bytes = 2 * H * (dk + dc) * pairs, pairs * dk * 2
+            hit = z["experts"] * (1 - (1 - z["top"] / z["experts"]) ** n)           # experts that some token chose, about
+            ff_flops, ff_bytes = 2 * n * z["top"] * 2 * z["ff"] * W, hit * 2 * z["ff"] * W * 2
+        else:
+            hkv = mixer.hkv
+            qkv = torch.randn((n, (H + 2 * hkv) * 128), device="cuda").to(torch.bfloat16)
+            o = torch.empty((n, H * 128), dtype=torch.bfloat16, device="cuda")
+            attn = lambda: mixer.attend(qkv, o, step, cache, table)
+            attn_flops, attn_bytes = 4 * H * 128 * pairs, pairs * 2 * hkv * 128 * 2
+            ff_flops, ff_bytes = 2 * n * 3 * inter * W, 3 * inter * W * 2
+        res = {}
+        for name, fn, flops, nbytes in (("attention kernel", attn, attn_flops, attn_bytes),
+                                        ("mixer", lambda: mixer.forward(x, step, cache), None, None),
+                                        ("feed-forward", lambda: ff.forward(x, step), ff_flops, ff_bytes)):
+            us = time_part(fn, reps, flush)
+            res[name] = {"us": round(us, 1)}
+            if flops is not None:
+                ideal = flops / (pk["bf16_tflops"] * 1e12) * 1e6 if phase == "prefill" else nbytes / (pk["hbm_gbs"] * 1e9) * 1e6
+                res[name].update(roofline_us=round(ideal, 1), of_roofline=round(ideal / us, 3))
+        driver.runner.check_kernels()
+        out[phase] = res
+        del driver
+        torch.cuda.empty_cache()
+    return out
+
+
+def design(name: str, layers, sizes, steps, warmup) -> int:
+    """`--design guronex`: prefill and decode throughput of the Guronex design at a few layer sizes beside the Qwen3
+    dense model of equal size (random weights, `--layers` layers, default 4), and the attention kernel, the mixer
+    and the feed-forward of one layer each alone with their rooflines."""
+    import torch
+    from jax_vllm_b200 import random_model, registry
+    if name != "guronex":
+        print(f"bench.py: no design {name!r}")
+        return 2
+    layers = layers or 4
+    pk, pk_src = peaks()
+    out = {"design": name, "layers": layers, "prefill_tokens": PREFILL_TOKENS, "decode_batch": 8, "context": CONTEXT,
+           "dtype": "bf16", "data": "synthetic (random weights, seed 5)", "peaks": pk, "peak_source": pk_src, "sizes": {}}
+    for tag in sizes:
+        z = DESIGN_SIZES[tag]
+        g_cfg, q_cfg = design_configs(z, layers)
+        row = {"guronex": {"config": {k: v for k, v in z.items()}}, "qwen3": {"config": {
+            "hidden": z["width"], "heads": z["heads"], "kv_heads": q_cfg["num_key_value_heads"], "head_dim": 128,
+            "intermediate": q_cfg["intermediate_size"]}}}
+        for kind, cfg in (("guronex", g_cfg), ("qwen3", q_cfg)):
+            model = random_model(registry.config_from_dict(cfg), seed=5, dtype="bf16", device="cuda:0")
+            with ClockSampler() as clocks:
+                pms = time_prefill(model, PREFILL_TOKENS, warmup=2, reps=5)
+                dms, launches, _, _ = time_decode(model, 8, steps, warmup)
+            row[kind].update(prefill_tok_s=round(PREFILL_TOKENS / (pms / 1e3), 1), prefill_ms=round(pms, 3),
+                             decode_tok_s=round(8 / (dms / 1e3), 1), decode_ms_per_step=round(dms, 4),
+                             decode_launches_per_step=launches, clocks=clocks.summary)
+            row[kind]["parts"] = design_parts(model, kind, z, q_cfg["intermediate_size"], 8, PREFILL_TOKENS, 7, pk)
+            del model
+            torch.cuda.empty_cache()
+        out["sizes"][tag] = row
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm():
     why = ("the reference (jllm) needs jax, jaxlib and equinox and the hatchling build backend; none is installed "
            "and none is in the offline wheelhouse, so it can neither be installed nor run here")
@@ -514,6 +655,10 @@ def main():
                     help="print every kernel of one replayed decode step at this batch with its start and end (use --layers)")
     ap.add_argument("--with-workloads", action="store_true",
                     help="after the headline run, also run the two serving workloads and add their lines under `workloads`")
+    ap.add_argument("--design", default=None, metavar="NAME",
+                    help="guronex: that design's prefill and decode throughput at a few layer sizes beside Qwen3 of "
+                         "equal size, with the rooflines of its attention and feed-forward (see design())")
+    ap.add_argument("--sizes", default="lite,mid,row576", help="with --design: which of its layer sizes, comma-separated")
     ap.add_argument("--micro-eager", action="store_true",
                     help="with --micro: plain launches instead of replays of a CUDA graph (for a profiler)")
     args = ap.parse_args()
@@ -524,6 +669,9 @@ def main():
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.design:
+        return design(args.design, args.layers, [t for t in args.sizes.split(",") if t], max(8, args.steps // 2),
+                      max(3, args.warmup))
     if args.timeline:
         return timeline(args.timeline, args.layers or 4, args.workload)
     if args.workload:

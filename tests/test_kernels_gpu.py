@@ -707,11 +707,11 @@ def test_mma_support_table_matches_the_library(ops):
 
 
 def test_attention_refuses_what_it_cannot_do(ops):
-    z = torch.zeros(1, 512, device=DEV)
+    z = torch.zeros(1, 1024, device=DEV)
     i = torch.zeros(2, dtype=torch.int32, device=DEV)
-    c = torch.zeros(1, 4, 1, 512, device=DEV)
-    with pytest.raises(ops.KernelError, match="outside what the kernel handles"):
-        ops.attn_simt(z, 512, z.clone(), c, c, i.view(1, 2), i, i[:1], i.view(1, 2), 1, 1, 1, 512, 0, 1.0)
+    c = torch.zeros(1, 4, 1, 1024, device=DEV)
+    with pytest.raises(ops.KernelError, match="outside what the kernel handles"):     # values of up to 512 elements
+        ops.attn_simt(z, 1024, z.clone(), c, c, i.view(1, 2), i, i[:1], i.view(1, 2), 1, 1, 1, 1024, 0, 1.0)
 
 
 # ------------------------------------------------------------------------- sampling
