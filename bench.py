@@ -518,16 +518,21 @@ def design_configs(z, layers, vocab=32000):
 
 
 def time_part(fn, reps, flush):
-    """Median device time (us) of `fn`, one launch sequence at a time, the L2 written over in between."""
+    """Median device time (us) of `fn`, captured into a CUDA graph (so that the host's launches do not count) and
+    replayed one at a time, the L2 written over in between."""
     import torch
     for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
         fn()
     times = []
     for _ in range(reps):
         flush.add_(1)
         torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record(); fn(); e.record()
+        s.record(); graph.replay(); e.record()
         torch.cuda.synchronize()
         times.append(s.elapsed_time(e) * 1e3)
     return statistics.median(times)

@@ -1,7 +1,7 @@
 // Routing of a mixture of experts, all in 32-bit.
 //
-// jv_moe_route, one warp per token:  z = W_router x (k ascending per lane, then a warp sum: the same for every
-// batch), s = softmax(z) over all experts; with groups, a group's score is its largest s and only experts of the
+// jv_moe_route, one warp per token, from the router logits z = W_router x (a product made before it, with 32-bit
+// accumulation and a 32-bit result):  s = softmax(z) over all experts; with groups, a group's score is its largest s and only experts of the
 // `keep` best groups stay; the `top` largest s among those are chosen, largest first (lowest index on a tie);
 // weight = s (divided by the chosen scores' sum if `renorm`).
 //
@@ -16,9 +16,8 @@
 namespace {
 constexpr int ROUTE_WARPS = 4;
 
-template <typename T, typename TW>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
-    const T* __restrict__ x, int x_stride, const TW* __restrict__ w, int n, int width, int experts, int top, int groups,
+    const float* __restrict__ z, int z_stride, int n, int experts, int top, int groups,
     int keep, int renorm, int* __restrict__ ids, float* __restrict__ weights) {
   extern __shared__ float smem[];                 // [ROUTE_WARPS][experts] scores, [ROUTE_WARPS][groups] group scores
   pdl_trigger();
@@ -28,14 +27,7 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(
   if (t >= n) return;
   float* s = smem + (size_t)warp * (experts + groups);
   float* gs = s + experts;
-  const T* xr = x + (size_t)t * x_stride;
-  for (int e = 0; e < experts; ++e) {
-    const TW* wr = w + (size_t)e * width;
-    float acc = 0.f;
-    for (int k = lane; k < width; k += 32) acc = fmaf(to_f32(xr[k]), to_f32(wr[k]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) s[e] = acc;
-  }
+  for (int e = lane; e < experts; e += 32) s[e] = z[(size_t)t * z_stride + e];
   __syncwarp();
   float mx = -INFINITY;
   for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, s[e]);
@@ -164,11 +156,9 @@ JV_EXPORT int jv_moe_gather_rows(const void* x, int dtype, int x_stride, const i
   return JV_ERR_UNSUPPORTED;
 }
 
-// x: [n, width] rows of x_stride elements (dtype); w: [experts, width] (w_dtype); ids: [n, top] int32;
-// weights: [n, top] float.
-JV_EXPORT int jv_moe_route(const void* x, int dtype, int x_stride, const void* w, int w_dtype, int n, int width,
-                           int experts, int top, int groups, int keep, int renorm, int* ids, float* weights,
-                           cudaStream_t stream) {
+// z: [n, experts] float rows of z_stride elements; ids: [n, top] int32; weights: [n, top] float.
+JV_EXPORT int jv_moe_route(const float* z, int z_stride, int n, int experts, int top, int groups, int keep, int renorm,
+                           int* ids, float* weights, cudaStream_t stream) {
   if (n == 0) return JV_OK;
   if (experts < 1 || top < 1 || top > experts || groups < 1 || experts % groups || keep < 1 || keep > groups ||
       top > keep * (experts / groups))
@@ -176,10 +166,8 @@ JV_EXPORT int jv_moe_route(const void* x, int dtype, int x_stride, const void* w
   const size_t smem = sizeof(float) * ROUTE_WARPS * (size_t)(experts + groups);
   if (smem > 48 * 1024) return JV_ERR_UNSUPPORTED;
   const int blocks = (n + ROUTE_WARPS - 1) / ROUTE_WARPS;
-  JV_DISPATCH_DTYPE(dtype, T, JV_DISPATCH_DTYPE(w_dtype, TW,
-      return jv_launch(moe_route_kernel<T, TW>, dim3(blocks), dim3(ROUTE_WARPS * 32), smem, stream, (const T*)x,
-                       x_stride, (const TW*)w, n, width, experts, top, groups, keep, renorm, ids, weights)));
-  return JV_ERR_UNSUPPORTED;
+  return jv_launch(moe_route_kernel, dim3(blocks), dim3(ROUTE_WARPS * 32), smem, stream, z, z_stride, n, experts, top,
+                   groups, keep, renorm, ids, weights);
 }
 
 // ids: [pairs] experts of the (token, choice) pairs, pairs = n * top; sorted_token: [max_tiles * tile];

@@ -486,7 +486,9 @@ def attn_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: tor
     """Paged causal attention of prompt portions on tcgen05 tensor cores with scores and output in tensor
     memory (csrc/attn_tcgen05.cu); `work` lists 128-row tiles of `attn_tcgen05_tokens_per_tile` tokens."""
     for t, nm in ((q, "q"), (out, "out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
-        _cuda(t, nm, torch.bfloat16, contiguous=(nm != "q"))
+        _cuda(t, nm, torch.bfloat16, contiguous=(nm not in ("q", "out")))     # q and out may be some heads of wider rows
+    if out.stride(1) != 1 or q.stride(1) != 1:
+        raise KernelError("q and out need unit column stride")
     for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (work, "work")):
         _cuda(t, nm, torch.int32)
     if n_work == 0:
@@ -538,7 +540,9 @@ def attn_decode_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cac
     q|k|v as it comes, and the kernel does what `rope_kv` does for these tokens itself (per-head norm,
     rotation at position start_pos, write of the new key and value into the caches)."""
     for t, nm in ((q, "q"), (out, "out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
-        _cuda(t, nm, torch.bfloat16, contiguous=(nm != "q"))
+        _cuda(t, nm, torch.bfloat16, contiguous=(nm not in ("q", "out")))     # q and out may be some heads of wider rows
+    if out.stride(1) != 1 or q.stride(1) != 1:
+        raise KernelError("q and out need unit column stride")
     for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (work, "work")):
         _cuda(t, nm, torch.int32)
     if n_work == 0:
@@ -915,20 +919,19 @@ def bmm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None)
 
 
 # ------------------------------------------------------------------- routed experts
-def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, groups: int, keep: int, renorm: bool):
-    """(ids [n, top] int32, weights [n, top] float32): router scores softmax(W x) in 32-bit, group-limited
-    choice of the `top` largest (csrc/moe_route.cu)."""
-    _cuda(x, "x", contiguous=False); _cuda(w_router, "router weight")
-    n, width = x.shape
-    experts = w_router.shape[0]
-    if w_router.shape != (experts, width) or x.stride(1) != 1:
-        raise KernelError("router weight does not fit the rows")
-    ids = torch.empty((n, top), dtype=torch.int32, device=x.device)
-    weights = torch.empty((n, top), dtype=torch.float32, device=x.device)
-    f = _fn("moe_route", "jv_moe_route", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                          c_int, c_int, c_void_p, c_void_p, c_void_p])
-    _check(f(x.data_ptr(), _code(x, "x"), x.stride(0), w_router.data_ptr(), _code(w_router, "router"), n, width,
-             experts, top, groups, keep, 1 if renorm else 0, ids.data_ptr(), weights.data_ptr(), _stream()), "moe_route")
+def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, renorm: bool):
+    """(ids [n, top] int32, weights [n, top] float32) from the router logits [n, experts] float32: softmax over all
+    experts, group-limited choice of the `top` largest, largest first (csrc/moe_route.cu)."""
+    _cuda(logits, "router logits", torch.float32, contiguous=False)
+    n, experts = logits.shape
+    if logits.stride(1) != 1:
+        raise KernelError("router logits need unit column stride")
+    ids = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    f = _fn("moe_route", "jv_moe_route", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                          c_void_p])
+    _check(f(logits.data_ptr(), logits.stride(0), n, experts, top, groups, keep, 1 if renorm else 0, ids.data_ptr(),
+             weights.data_ptr(), _stream()), "moe_route")
     return ids, weights
 
 

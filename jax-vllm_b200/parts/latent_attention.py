@@ -100,11 +100,19 @@ class LatentAttention(Part):
 
     FOREVER = 1 << 30
 
+    def _head_group(self) -> int:
+        """The tcgen05 kernels take up to 16 query heads on one key/value head: more heads go through them in
+        equal groups of the largest size up to 16 that divides their number (every group reads the same cache)."""
+        return max(g for g in range(1, min(self.h, 16) + 1) if self.h % g == 0)
+
     def tile_classes(self, page_size: int):
         small = (ops.attn_mma_tokens_per_tile if self.use_mma else ops.attn_simt_tokens_per_tile)(self.h, 1)
-        if ops.attn_tcgen05_supports(self.ctx.dtype, self.dk, self.h, 1, page_size, 0):
-            big = ops.attn_tcgen05_tokens_per_tile(self.h, 1)
-            return [(small, 2, big), (big, big, self.FOREVER)]
+        g = self._head_group()
+        if ops.attn_tcgen05_supports(self.ctx.dtype, self.dk, g, 1, page_size, 0):
+            big = ops.attn_tcgen05_tokens_per_tile(g, 1)
+            if big > small:
+                return [(small, 2, big), (big, big, self.FOREVER)]
+            return [(big, 2, self.FOREVER)] if big == small else [(small, 2, self.FOREVER)]
         return [(small, 2, self.FOREVER)]
 
     # ----------------------------------------------------------------------- step
@@ -144,17 +152,23 @@ class LatentAttention(Part):
             out = torch.empty((n, H * self.dc), dtype=q.dtype, device=q.device)
             extra, per_head = {"v_dim": self.dc}, self.dc
             kernel = ops.attn_simt
-        for cls in self.tile_classes(cache.k.shape[1]):
+        g = self._head_group()
+        page = cache.k.shape[1]
+        groups = [(q[:, i * dk:(i + g) * dk], out[:, i * dk:(i + g) * dk]) for i in range(0, H, g)] if self.use_mma else []
+        big = ops.attn_tcgen05_tokens_per_tile(g, 1) if ops.attn_tcgen05_supports(self.ctx.dtype, dk, g, 1, page, 0) else 0
+        for cls in self.tile_classes(page):
             work, n_work = step.tile_work[cls]
             if not n_work:
                 continue
-            if cls[2] == self.FOREVER and cls[1] > 2:      # the class of whole 128-row tiles
-                ops.attn_tcgen05(q, q.stride(0), out, *common, work, n_work, H, 1, dk, self.spec.scale)
+            if big and cls[0] == big:                      # whole tiles of the tcgen05 kernel, one head group at a time
+                for qg, og in groups:
+                    ops.attn_tcgen05(qg, q.stride(0), og, *common, work, n_work, g, 1, dk, self.spec.scale)
             else:
                 kernel(q, q.stride(0), out, *common, work, n_work, H, 1, dk, 0, self.spec.scale, **extra)
         dwork, n_dec = step.decode_work
-        if n_dec and self.use_mma and ops.attn_decode_tcgen05_supports(self.ctx.dtype, dk, H, 1, cache.k.shape[1], 0, n_dec):
-            ops.attn_decode_tcgen05(q, q.stride(0), out, *common, dwork, n_dec, H, 1, dk, self.spec.scale)
+        if n_dec and self.use_mma and ops.attn_decode_tcgen05_supports(self.ctx.dtype, dk, g, 1, page, 0, n_dec):
+            for qg, og in groups:
+                ops.attn_decode_tcgen05(qg, q.stride(0), og, *common, dwork, n_dec, g, 1, dk, self.spec.scale)
         elif n_dec:
             split = self.ctx.decode_split_size
             n_splits = max(1, -(-step.max_seq_len // split))

@@ -1,6 +1,7 @@
 """A mixture of small feed-forward experts, each down(act(up(x))), no biases.
 
-    ids, w   = route(x)                 softmax scores in 32-bit, group-limited choice of the top_k (csrc/moe_route.cu)
+    z        = x @ W_router^T           32-bit accumulation and result (ops.linear)
+    ids, w   = route(z)                 softmax scores in 32-bit, group-limited choice of the top_k (csrc/moe_route.cu)
     order    = pairs sorted by expert   every expert's rows padded to a row tile (csrc/moe_route.cu, jv_moe_align)
     a        = act(x[token] @ W_up_e^T) grouped product, rows gathered as they are read, activation in its epilogue
     y        = a @ W_down_e^T           grouped product
@@ -20,7 +21,7 @@ from .registry import register_feed_forward
 
 
 class RoutedExperts(Part):
-    kernels = ("moe_route", "moe_gemm_simt")
+    kernels = ("moe_route", "moe_gemm_simt", "gemm_simt")
 
     def __init__(self, spec, prefix, ctx):
         if spec.activation != "gelu":
@@ -44,7 +45,7 @@ class RoutedExperts(Part):
 
     def bind(self, tensors):
         p, s = self.prefix, self.spec
-        self.w_router = tensors[f"{p}.router"].contiguous()
+        self.w_router = self.compute_weight(tensors[f"{p}.router"], self.ctx).contiguous()
         ups = [self.compute_weight(tensors[f"{p}.e{e}.up"], self.ctx) for e in range(s.num_experts)]
         downs = [self.compute_weight(tensors[f"{p}.e{e}.down"], self.ctx) for e in range(s.num_experts)]
         if len({m.dtype for m in ups + downs}) > 1:
@@ -52,7 +53,7 @@ class RoutedExperts(Part):
         self.w_up = torch.stack(ups).contiguous()
         self.w_down = torch.stack(downs).contiguous()
         if self._tensor_cores():
-            self.kernels = ("moe_route", "gemm_tcgen05")
+            self.kernels = ("moe_route", "gemm_tcgen05", "gemm_simt")
 
     # The grouped tcgen05 product works on 128-row tiles of 256 columns: it is taken for bfloat16 experts whose inner
     # sizes it can address (multiples of 8) and whose matrices are at least this wide; smaller ones, and the 32-bit
@@ -66,7 +67,8 @@ class RoutedExperts(Part):
 
     def forward(self, x, step):
         s, dt = self.spec, self.ctx.dtype
-        ids, weights = ops.moe_route(x, self.w_router, s.top_k, s.n_groups, s.keep_groups, s.renormalize)
+        logits = ops.linear(x, self.w_router, torch.float32)       # 32-bit accumulation, 32-bit result
+        ids, weights = ops.moe_route(logits, s.top_k, s.n_groups, s.keep_groups, s.renormalize)
         if self._tensor_cores():
             _, pos_of, tile_expert = ops.moe_align(ids, s.num_experts, ops.MOE_TCGEN05_TILE)
             rows = ops.moe_gather_rows(x, pos_of, tile_expert.numel() * ops.MOE_TCGEN05_TILE)

@@ -59,8 +59,10 @@ GE = config(128, 64, [layer(mixer(2, 32, 64, 32, 320), moe(4, 2, 32))], eps=1e-5
 # experts of 128 and more (the grouped tcgen05 product in bfloat16), one size no multiple of its tiles
 GF = config(256, 128, [layer(mixer(4, 16, 16, 32, 48), moe(8, 2, 128, (2, 1))),
                        layer(mixer(4, 16, 16, 32, 48, kv_from=0), moe(8, 3, 136))], eps=1e-5, mult=0.5, side=8)
-CONFIGS = {"ga": GA, "gb": GB, "gc": GC, "gd": GD, "ge": GE, "gf": GF}
-PAGE = {"ga": 16, "gb": 8, "gc": 16, "gd": 4, "ge": 32, "gf": 16}
+# 24 heads on a cache row of 128: the tcgen05 attention takes them as two groups of 12
+GG = config(180, 96, [layer(mixer(24, 8, 48, 8, 80), moe(4, 2, 16))], eps=1e-5, mult=0.6)
+CONFIGS = {"ga": GA, "gb": GB, "gc": GC, "gd": GD, "ge": GE, "gf": GF, "gg": GG}
+PAGE = {"ga": 16, "gb": 8, "gc": 16, "gd": 4, "ge": 32, "gf": 16, "gg": 16}
 
 
 def tensor_shapes(c: dict) -> dict:

@@ -23,7 +23,7 @@ from tests.util import portions, prefix_then_single, random_tokens, whole
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 LENGTHS = {"ga": [70, 45, 100, 33], "gb": [90, 38, 64, 51], "gc": [200, 70, 150, 40], "gd": [61, 40, 83, 35],
-           "ge": [80, 37, 50, 20], "gf": [150, 40, 90, 30]}
+           "ge": [80, 37, 50, 20], "gf": [150, 40, 90, 30], "gg": [150, 40, 90, 30]}
 
 
 CLOSE_CALL = 0.1       # a difference of router logits below which bfloat16 may choose another expert
@@ -170,7 +170,7 @@ def test_router_alone(experts, top, groups, width):
         rt["groups"] = {"count": groups[0], "keep": groups[1]}
     chosen, weight = gp.route(x.double(), w.double(), rt)
     n, keep = groups or (1, 1)
-    ids, wts = ops.moe_route(x.cuda(), w.cuda(), top, n, keep, False)
+    ids, wts = ops.moe_route(ops.linear(x.cuda(), w.cuda(), torch.float32), top, n, keep, False)
     assert ids.cpu().tolist() == chosen.tolist()                # largest first, as the oracle's topk gives them
     assert torch.allclose(wts.cpu().double(), weight, rtol=1e-5, atol=1e-7)
     assert not torch.allclose(wts.sum(dim=1).cpu(), torch.ones(70))          # the scores are not renormalised
