@@ -540,8 +540,8 @@ def time_part(fn, reps, flush):
 
 def design_parts(model, kind, z, inter, batch, tokens, reps, pk):
     """The attention kernel alone, the whole mixer and the whole feed-forward of layer 0: one prompt of `tokens`
-    tokens, then one decode step of `batch` requests at CONTEXT tokens; each with its roofline (FLOPs over the
-    measured bf16 peak for the prompt, bytes over the measured copy bandwidth for the decode step)."""
+    tokens, then one decode step of `batch` requests at CONTEXT tokens; each with its roofline (the slower of its
+    FLOPs at the measured bf16 peak and its bytes, weights and cache rows read once, at the measured copy bandwidth)."""
     import torch
     from jax_vllm_b200 import make_driver
     from jax_vllm_b200.engine import StepEntry
@@ -574,7 +574,8 @@ def design_parts(model, kind, z, inter, batch, tokens, reps, pk):
             dk, dc = z["rank"] + z["rot"], z["rank"]
             q = torch.randn((n, H * dk), device="cuda").to(torch.bfloat16)
             attn = lambda: mixer.attend(q, step, cache, table)
-            attn_flops, attn_bytes = 2 * H * (dk + dc) * pairs, pairs * dk * 2
+            keys = tokens if phase == "prefill" else batch * (CONTEXT + 1)          # cache rows read, each once
+            attn_flops, attn_bytes = 2 * H * (dk + dc) * pairs, keys * dk * 2 + n * H * (dk + dc) * 2
             hit = z["experts"] * (1 - (1 - z["top"] / z["experts"]) ** n)           # experts that some token chose, about
             ff_flops, ff_bytes = 2 * n * z["top"] * 2 * z["ff"] * W, hit * 2 * z["ff"] * W * 2
         else:
@@ -582,7 +583,8 @@ def design_parts(model, kind, z, inter, batch, tokens, reps, pk):
             qkv = torch.randn((n, (H + 2 * hkv) * 128), device="cuda").to(torch.bfloat16)
             o = torch.empty((n, H * 128), dtype=torch.bfloat16, device="cuda")
             attn = lambda: mixer.attend(qkv, o, step, cache, table)
-            attn_flops, attn_bytes = 4 * H * 128 * pairs, pairs * 2 * hkv * 128 * 2
+            keys = tokens if phase == "prefill" else batch * (CONTEXT + 1)
+            attn_flops, attn_bytes = 4 * H * 128 * pairs, keys * 2 * hkv * 128 * 2 + n * H * 128 * 2 * 2
             ff_flops, ff_bytes = 2 * n * 3 * inter * W, 3 * inter * W * 2
         res = {}
         for name, fn, flops, nbytes in (("attention kernel", attn, attn_flops, attn_bytes),
@@ -591,8 +593,11 @@ def design_parts(model, kind, z, inter, batch, tokens, reps, pk):
             us = time_part(fn, reps, flush)
             res[name] = {"us": round(us, 1)}
             if flops is not None:
-                ideal = flops / (pk["bf16_tflops"] * 1e12) * 1e6 if phase == "prefill" else nbytes / (pk["hbm_gbs"] * 1e9) * 1e6
-                res[name].update(roofline_us=round(ideal, 1), of_roofline=round(ideal / us, 3))
+                # the slower of the arithmetic at the measured bf16 peak and the bytes at the measured copy bandwidth
+                t_flops, t_bytes = flops / (pk["bf16_tflops"] * 1e12) * 1e6, nbytes / (pk["hbm_gbs"] * 1e9) * 1e6
+                ideal = max(t_flops, t_bytes)
+                res[name].update(roofline_us=round(ideal, 1), bound="flops" if t_flops >= t_bytes else "bytes",
+                                 of_roofline=round(ideal / us, 3))
         driver.runner.check_kernels()
         out[phase] = res
         del driver

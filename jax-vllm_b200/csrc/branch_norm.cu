@@ -12,6 +12,8 @@
 #include "common.cuh"
 
 namespace {
+constexpr int MAX_PICKS = 64;     // rows that one row of a branch may be the weighted sum of
+
 template <typename TD, typename TW, typename TX>
 __global__ void branch_norm_add_kernel(float* __restrict__ h, const TD* __restrict__ y, size_t part_stride, int parts,
                                        const int* __restrict__ pick, const float* __restrict__ coef, int y_rows,
@@ -19,21 +21,27 @@ __global__ void branch_norm_add_kernel(float* __restrict__ h, const TD* __restri
                                        float mult, int* __restrict__ status) {
   extern __shared__ float row[];
   __shared__ float scratch[33];
+  __shared__ int pick_s[MAX_PICKS];
+  __shared__ float coef_s[MAX_PICKS];
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x;
+  if (pick != nullptr) {
+    // which rows, and their weights, once for the block; a row outside the tensor is left out (and reported)
+    if (threadIdx.x < parts) {
+      int src = pick[(size_t)r * parts + threadIdx.x];
+      if (src < 0 || src >= y_rows) { atomicOr(status, JV_STATUS_BAD_ROW); src = -1; }
+      pick_s[threadIdx.x] = src;
+      coef_s[threadIdx.x] = coef[(size_t)r * parts + threadIdx.x];
+    }
+    __syncthreads();
+  }
   float ss = 0.f;
   for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
     float v = 0.f;
     if (pick != nullptr) {
-      for (int s = 0; s < parts; ++s) {
-        const int src = pick[(size_t)r * parts + s];
-        if (src < 0 || src >= y_rows) {
-          if (c == 0) atomicOr(status, JV_STATUS_BAD_ROW);
-          continue;
-        }
-        v = fmaf(coef[(size_t)r * parts + s], to_f32(y[(size_t)src * hidden + c]), v);
-      }
+      for (int s = 0; s < parts; ++s)
+        if (pick_s[s] >= 0) v = fmaf(coef_s[s], to_f32(y[(size_t)pick_s[s] * hidden + c]), v);
     } else {
       v = to_f32(y[(size_t)r * hidden + c]);
       for (int s = 1; s < parts; ++s) v += to_f32(y[s * part_stride + (size_t)r * hidden + c]);
@@ -89,7 +97,7 @@ JV_EXPORT int jv_branch_norm_add(float* h, const void* y, int y_dtype, long long
                                  int weight_dtype, void* x_out, int x_dtype, int n, int hidden, float eps, float mult,
                                  int* status, cudaStream_t stream) {
   if (n == 0) return JV_OK;
-  if (parts < 1 || (size_t)hidden * sizeof(float) > 200 * 1024) return JV_ERR_UNSUPPORTED;
+  if (parts < 1 || (pick != nullptr && parts > MAX_PICKS) || (size_t)hidden * sizeof(float) > 200 * 1024) return JV_ERR_UNSUPPORTED;
   int threads = 64;
   while (threads < 512 && threads * 4 < hidden) threads *= 2;
   const size_t smem = (size_t)hidden * sizeof(float);

@@ -84,12 +84,15 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
                                                                   const __grid_constant__ CUtensorMap b_map, void* C,
                                                                   int ldc, int M, int N, int K, int* status,
                                                                   const int* __restrict__ tile_expert,
-                                                                  int expert_rows) {
+                                                                  int expert_rows, const int* __restrict__ used_row_tiles) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   Shared* sh = reinterpret_cast<Shared*>(tiles + STAGES * STAGE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  // grouped: the row tiles in use are the first `*used_row_tiles` (the rest would be skipped one by one: counting
+  // only those in use shares the work evenly among the blocks)
+  const int tiles_m = used_row_tiles != nullptr ? min(*used_row_tiles, (M + BM - 1) / BM) : (M + BM - 1) / BM;
+  const int tiles_n = (N + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
   const int k_blocks = (K + BK - 1) / BK;
 
@@ -292,7 +295,7 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int k, int ld, int b
 
 template <int EPI>
 int launch(const CUtensorMap& a, const CUtensorMap& b, void* C, int ldc, int M, int N, int K, int* status,
-           cudaStream_t stream, const int* tile_expert = nullptr, int expert_rows = 0) {
+           cudaStream_t stream, const int* tile_expert = nullptr, int expert_rows = 0, const int* used_row_tiles = nullptr) {
   constexpr size_t smem = STAGES * STAGE_BYTES + sizeof(Shared) + 1024;
   static bool ready[JV_MAX_DEVICES];
   static int sm_count[JV_MAX_DEVICES];
@@ -310,7 +313,7 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, void* C, int ldc, int M, 
   const int sms = sm_count[dev];
   const int n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const int blocks = n_tiles < sms ? n_tiles : sms;
-  gemm_tcgen05_kernel<EPI><<<blocks, THREADS, smem, stream>>>(a, b, C, ldc, M, N, K, status, tile_expert, expert_rows);
+  gemm_tcgen05_kernel<EPI><<<blocks, THREADS, smem, stream>>>(a, b, C, ldc, M, N, K, status, tile_expert, expert_rows, used_row_tiles);
   return jv_check_launch();
 }
 }  // namespace
@@ -341,17 +344,18 @@ JV_EXPORT int jv_moe_gemm_tcgen05_tile() { return BM; }
 // padding may hold anything: a row of C depends on its own row of A only); B: [experts, N, K] bfloat16, contiguous
 // experts, rows of ldb; C: [max_tiles * 128, N] bfloat16 rows of ldc; epilogue 0: none, 3: the exact gelu.
 // A column tile that reaches beyond N reads the next expert's rows (or zeros); its columns beyond N are not written.
+// used_row_tiles: one int on the device, the number of leading row tiles that have an expert, or null.
 JV_EXPORT int jv_moe_gemm_tcgen05(const void* A, int lda, const void* B, int ldb, int experts, const int* tile_expert,
-                                  int max_tiles, void* C, int ldc, int N, int K, int epilogue, int* status,
-                                  cudaStream_t stream) {
+                                  int max_tiles, const int* used_row_tiles, void* C, int ldc, int N, int K, int epilogue,
+                                  int* status, cudaStream_t stream) {
   if (max_tiles == 0 || N == 0) return JV_OK;
   if (K < 8 || (K % 8) || (lda % 8) || (ldb % 8) || ((uintptr_t)A % 16) || ((uintptr_t)B % 16)) return JV_ERR_UNSUPPORTED;
   const int M = max_tiles * BM;
   CUtensorMap a_map, b_map;
   if (!make_map(&a_map, A, M, K, lda, BM) || !make_map(&b_map, B, experts * N, K, ldb, BN)) return JV_ERR_UNSUPPORTED;
   switch (epilogue) {
-    case EPI_BF16: return launch<EPI_BF16>(a_map, b_map, C, ldc, M, N, K, status, stream, tile_expert, N);
-    case EPI_GELU: return launch<EPI_GELU>(a_map, b_map, C, ldc, M, N, K, status, stream, tile_expert, N);
+    case EPI_BF16: return launch<EPI_BF16>(a_map, b_map, C, ldc, M, N, K, status, stream, tile_expert, N, used_row_tiles);
+    case EPI_GELU: return launch<EPI_GELU>(a_map, b_map, C, ldc, M, N, K, status, stream, tile_expert, N, used_row_tiles);
   }
   return JV_ERR_UNSUPPORTED;
 }

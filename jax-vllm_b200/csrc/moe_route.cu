@@ -7,7 +7,8 @@
 //
 // jv_moe_align, one block: puts the (token, choice) pairs in the order of their experts, every expert's run
 // padded to a multiple of `tile` rows so that a row tile of the grouped products belongs to one expert:
-//   sorted_token[pos] = token (-1: padding), pos_of[token*top + k] = pos, tile_expert[tile] = expert (-1: unused).
+//   sorted_token[pos] = token (-1: padding), pos_of[token*top + k] = pos, tile_expert[tile] = expert (-1: unused),
+//   tile_expert[max_tiles] = number of tiles in use (they are the first ones).
 // Which of an expert's rows a pair gets depends on the order of arrival; no result depends on it, since every
 // row of a product is computed alone.
 #include "common.cuh"
@@ -116,6 +117,7 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
       for (int k = 0; k < tiles; ++k) tile_expert[row / tile + k] = e;
       row += tiles * tile;
     }
+    tile_expert[max_tiles] = row / tile;          // the row tiles in use are the first this many
   }
   __syncthreads();
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
@@ -171,7 +173,7 @@ JV_EXPORT int jv_moe_route(const float* z, int z_stride, int n, int experts, int
 }
 
 // ids: [pairs] experts of the (token, choice) pairs, pairs = n * top; sorted_token: [max_tiles * tile];
-// pos_of: [pairs]; tile_expert: [max_tiles], max_tiles >= pairs / tile + experts.
+// pos_of: [pairs]; tile_expert: [max_tiles + 1], max_tiles >= pairs / tile + experts.
 JV_EXPORT int jv_moe_align(const int* ids, int pairs, int top, int experts, int tile, int max_tiles, int* sorted_token,
                            int* pos_of, int* tile_expert, int* status, cudaStream_t stream) {
   if (pairs == 0) return JV_OK;

@@ -421,6 +421,47 @@ def attn_mma_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
     return 64 // min(g, 16)
 
 
+def attn_latent_mma_supports(dtype: torch.dtype, dk: int, dv: int) -> bool:
+    """Whether the tensor-core attention over a latent cache takes rows of dk with values of dv
+    (csrc/attn_latent_mma.cu): bfloat16, dk a multiple of 8 up to about 640, dv up to 512."""
+    if dtype != torch.bfloat16 or dk % 8 or not 1 <= dv <= min(dk, 512):
+        return False
+    dkp = -(-dk // 16) * 16
+    cols = (32 if dv <= 32 else 64 if dv <= 64 else 128 if dv <= 128 else 256) * (2 if dv > 256 else 1)
+    return 2 * (64 * (dkp + 8) + 2 * 32 * (max(dkp, cols) + 8)) <= 220 * 1024
+
+
+def attn_latent_mma_tokens_per_tile(n_heads: int) -> int:
+    return 64 // min(n_heads, 64)
+
+
+def attn_latent_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor,
+                    cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor, n_work: int, n_heads: int,
+                    dk: int, dv: int, scale: float, split_size: int = 0, n_splits: int = 0) -> None:
+    """Paged causal attention with one key/value head whose key is the cache row [dk] and whose value is the row's
+    first dv elements, on the tensor cores (csrc/attn_latent_mma.cu); `work` and the split arguments as for
+    `attn_simt`, with `attn_latent_mma_tokens_per_tile` tokens per prompt tile; out has dv elements per head."""
+    for t, nm in ((q, "q"), (out, "out"), (cache, "cache")):
+        _cuda(t, nm, torch.bfloat16, contiguous=(nm != "q"))
+    for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (work, "work")):
+        _cuda(t, nm, torch.int32)
+    if n_work == 0:
+        return
+    if cache.shape[2:] != (1, dk):
+        raise KernelError(f"cache shape {tuple(cache.shape)} does not fit rows of {dk}")
+    part_o = part_ml = None
+    if n_splits > 0:
+        part_o = torch.empty(n_work * n_heads * n_splits * dv, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(n_work * n_heads * n_splits * 2, dtype=torch.float32, device=q.device)
+    f = _fn("attn_latent_mma", "jv_attn_latent_mma", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                      c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                      c_int, c_float, c_int, c_int, c_void_p, c_void_p])
+    _check(f(q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), _ptr(part_o), _ptr(part_ml), cache.data_ptr(),
+             block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(),
+             n_work, n_heads, dk, dv, cache.shape[1], cache.shape[0], float(scale), int(split_size), int(n_splits),
+             _status_ptr(q.device), _stream()), "attn_latent_mma", launches=2 if n_splits > 0 else 1)
+
+
 _counters: dict[int, torch.Tensor] = {}
 _counters_outgrown: list = []     # smaller buffers that a captured graph may still point at: never freed
 
@@ -937,19 +978,20 @@ def moe_route(logits: torch.Tensor, top: int, groups: int, keep: int, renorm: bo
 
 def moe_align(ids: torch.Tensor, experts: int, tile: int):
     """The (token, choice) pairs in the order of their experts, each expert's run padded to `tile` rows:
-    (sorted_token [max_tiles * tile] (-1: padding), pos_of [n, top], tile_expert [max_tiles] (-1: unused))."""
+    (sorted_token [max_tiles * tile] (-1: padding), pos_of [n, top], tile_expert [max_tiles] (-1: unused), and
+    a one-element tensor: how many leading tiles are in use)."""
     _cuda(ids, "ids", torch.int32)
     n, top = ids.shape
     pairs = n * top
     max_tiles = -(-(pairs + experts * (tile - 1)) // tile)
     sorted_token = torch.empty(max_tiles * tile, dtype=torch.int32, device=ids.device)
     pos_of = torch.empty((n, top), dtype=torch.int32, device=ids.device)
-    tile_expert = torch.empty(max_tiles, dtype=torch.int32, device=ids.device)
+    tile_expert = torch.empty(max_tiles + 1, dtype=torch.int32, device=ids.device)
     f = _fn("moe_route", "jv_moe_align", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_void_p])
     _check(f(ids.data_ptr(), pairs, top, experts, tile, max_tiles, sorted_token.data_ptr(), pos_of.data_ptr(),
              tile_expert.data_ptr(), _status_ptr(ids.device), _stream()), "moe_align")
-    return sorted_token, pos_of, tile_expert
+    return sorted_token, pos_of, tile_expert[:max_tiles], tile_expert[max_tiles:]
 
 
 MOE_ACTS = {None: 0, "gelu": 1}
@@ -1011,19 +1053,23 @@ def moe_gemm_tcgen05_supports(dtype: torch.dtype, w: torch.Tensor) -> bool:
             and w.shape[2] % 8 == 0 and w.shape[2] >= 8 and w.data_ptr() % 16 == 0)
 
 
-def moe_gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, act: str | None = None) -> torch.Tensor:
+def moe_gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, act: str | None = None,
+                     used_tiles: torch.Tensor | None = None) -> torch.Tensor:
     """Grouped product on tcgen05 (csrc/gemm_tcgen05.cu): row pos of the result, in a 128-row tile of expert e, is
-    act(a[pos] @ w[e].T); a [max_tiles * 128, K] bfloat16 in the order of the experts, w [experts, N, K]."""
+    act(a[pos] @ w[e].T); a [max_tiles * 128, K] bfloat16 in the order of the experts, w [experts, N, K];
+    `used_tiles`: one int32 on the device, how many leading tiles have an expert."""
     _cuda(a, "a", torch.bfloat16); _cuda(w, "w", torch.bfloat16); _cuda(tile_expert, "tile_expert", torch.int32)
+    if used_tiles is not None:
+        _cuda(used_tiles, "used_tiles", torch.int32)
     max_tiles = tile_expert.numel()
     experts, n_out, k = w.shape
     if a.shape != (max_tiles * MOE_TCGEN05_TILE, k):
         raise KernelError("grouped product: rows do not fit the tiles")
     out = torch.empty((a.shape[0], n_out), dtype=torch.bfloat16, device=a.device)
-    f = _fn("gemm_tcgen05", "jv_moe_gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
-                                                    c_int, c_int, c_int, c_void_p, c_void_p])
+    f = _fn("gemm_tcgen05", "jv_moe_gemm_tcgen05", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                                    c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(f(a.data_ptr(), a.stride(0), w.data_ptr(), w.stride(1), experts, tile_expert.data_ptr(), max_tiles,
-             out.data_ptr(), out.stride(0), n_out, k, GEMM_EPILOGUES["gelu" if act == "gelu" else "bf16"],
+             _ptr(used_tiles), out.data_ptr(), out.stride(0), n_out, k, GEMM_EPILOGUES["gelu" if act == "gelu" else "bf16"],
              _status_ptr(a.device), _stream()), "moe_gemm_tcgen05")
     return out
 

@@ -47,6 +47,10 @@ class LatentAttention(Part):
         self.writes_cache = True          # set False by the model for a layer that reads another's cache
         # bfloat16 with a row size the tensor-core kernels are built for; else the CUDA-core kernel
         self.use_mma = ops.attn_mma_supports(ctx.dtype, self.dk)
+        # other row sizes in bfloat16: the tensor-core kernel written for latent rows (key = the row, value = its start)
+        self.use_latent_mma = not self.use_mma and ops.attn_latent_mma_supports(ctx.dtype, self.dk, self.dc)
+        if self.use_latent_mma:
+            self.kernels = ("latent_prepare", "attn_latent_mma", "gemm_simt", "linear_skinny")
         if self.use_mma:
             self.kernels = ("latent_prepare", "attn_mma", "gemm_simt", "linear_skinny")
             if self.dk == 128:
@@ -106,6 +110,8 @@ class LatentAttention(Part):
         return max(g for g in range(1, min(self.h, 16) + 1) if self.h % g == 0)
 
     def tile_classes(self, page_size: int):
+        if self.use_latent_mma:
+            return [(ops.attn_latent_mma_tokens_per_tile(self.h), 2, self.FOREVER)]
         small = (ops.attn_mma_tokens_per_tile if self.use_mma else ops.attn_simt_tokens_per_tile)(self.h, 1)
         g = self._head_group()
         if ops.attn_tcgen05_supports(self.ctx.dtype, self.dk, g, 1, page_size, 0):
@@ -143,6 +149,18 @@ class LatentAttention(Part):
         """One key/value head: the cache row is the key, its leading latent part the value."""
         n, H, dk = step.n_tokens, self.h, self.dk
         common = (cache.k, cache.k, table, step.cu_seqlens, step.start_pos)
+        if self.use_latent_mma:
+            out = torch.empty((n, H * self.dc), dtype=q.dtype, device=q.device)
+            args = (cache.k, table, step.cu_seqlens, step.start_pos)
+            for cls in self.tile_classes(cache.k.shape[1]):
+                work, n_work = step.tile_work[cls]
+                ops.attn_latent_mma(q, q.stride(0), out, *args, work, n_work, H, dk, self.dc, self.spec.scale)
+            dwork, n_dec = step.decode_work
+            if n_dec:
+                split = self.ctx.decode_split_size
+                ops.attn_latent_mma(q, q.stride(0), out, *args, dwork, n_dec, H, dk, self.dc, self.spec.scale,
+                                    split_size=split, n_splits=max(1, -(-step.max_seq_len // split)))
+            return out.view(n, H, self.dc)
         if self.use_mma:
             # the tensor-core kernels take keys and values of one size: they return whole rows, the latent part leads
             out = torch.empty((n, H * dk), dtype=q.dtype, device=q.device)

@@ -70,11 +70,11 @@ class RoutedExperts(Part):
         logits = ops.linear(x, self.w_router, torch.float32)       # 32-bit accumulation, 32-bit result
         ids, weights = ops.moe_route(logits, s.top_k, s.n_groups, s.keep_groups, s.renormalize)
         if self._tensor_cores():
-            _, pos_of, tile_expert = ops.moe_align(ids, s.num_experts, ops.MOE_TCGEN05_TILE)
+            _, pos_of, tile_expert, used = ops.moe_align(ids, s.num_experts, ops.MOE_TCGEN05_TILE)
             rows = ops.moe_gather_rows(x, pos_of, tile_expert.numel() * ops.MOE_TCGEN05_TILE)
-            act = ops.moe_gemm_tcgen05(rows, self.w_up, tile_expert, act="gelu")
-            return ops.PickedRows(ops.moe_gemm_tcgen05(act, self.w_down, tile_expert), pos_of, weights)
-        sorted_token, pos_of, tile_expert = ops.moe_align(ids, s.num_experts, ops.moe_gemm_simt_tile())
+            act = ops.moe_gemm_tcgen05(rows, self.w_up, tile_expert, act="gelu", used_tiles=used)
+            return ops.PickedRows(ops.moe_gemm_tcgen05(act, self.w_down, tile_expert, used_tiles=used), pos_of, weights)
+        sorted_token, pos_of, tile_expert, _ = ops.moe_align(ids, s.num_experts, ops.moe_gemm_simt_tile())
         act = ops.moe_gemm_simt(x, sorted_token, self.w_up, tile_expert, dt, act="gelu")
         y = ops.moe_gemm_simt(act, None, self.w_down, tile_expert, dt)
         return ops.PickedRows(y, pos_of, weights)

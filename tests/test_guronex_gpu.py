@@ -296,6 +296,50 @@ def test_latent_prepare_alone(dtype):
     assert (gq[:, :, :dc] == 0).all()                        # the latent part belongs to the batched product
 
 
+@pytest.mark.parametrize("heads,dk,dv", [(3, 48, 40), (5, 96, 72), (2, 384, 320), (16, 576, 512), (70, 24, 16), (1, 160, 128)])
+def test_latent_tensor_core_attention_alone(heads, dk, dv):
+    """csrc/attn_latent_mma.cu against the CUDA-core kernel (32-bit arithmetic) on the same bfloat16 rows: three
+    entries with earlier context (a prompt portion over several tiles, a short one, a single token split along its
+    keys), pages in a scrambled order, unowned places filled with NaN."""
+    from jax_vllm_b200 import ops
+    g = torch.Generator().manual_seed(heads * dk)
+    P, n_pages = 8, 64
+    ctx, new = [37, 0, 130], [45, 3, 1]
+    cache = torch.full((n_pages, P, 1, dk), float("nan"), dtype=torch.bfloat16)
+    width = max(-(-(c + q) // P) for c, q in zip(ctx, new))
+    table = torch.full((3, width), -1, dtype=torch.int32)
+    free = torch.randperm(n_pages, generator=g).tolist()
+    for e, (c, q) in enumerate(zip(ctx, new)):
+        for i in range(-(-(c + q) // P)):
+            table[e, i] = free.pop()
+            fill = min(P, c + q - i * P)
+            cache[table[e, i], :fill] = torch.randn((fill, 1, dk), generator=g).to(torch.bfloat16)
+    n = sum(new)
+    q = (torch.randn((n, heads * dk), generator=g) * 0.5).to(torch.bfloat16).cuda()
+    cu = torch.tensor([0, 45, 48, 49], dtype=torch.int32).cuda()
+    start = torch.tensor(ctx, dtype=torch.int32).cuda()
+    cache_d, table_d = cache.cuda(), table.cuda()
+    tpt = ops.attn_latent_mma_tokens_per_tile(heads)
+    work = torch.tensor([(e, t) for e in (0, 1) for t in range(0, new[e], tpt)], dtype=torch.int32).cuda()
+    spt = ops.attn_simt_tokens_per_tile(heads, 1)
+    work_s = torch.tensor([(e, t) for e in (0, 1) for t in range(0, new[e], spt)], dtype=torch.int32).cuda()
+    dwork = torch.tensor([(2, 0)], dtype=torch.int32).cuda()
+    scale = dk ** -0.5
+    got = torch.zeros((n, heads * dv), dtype=torch.bfloat16).cuda()
+    want = torch.zeros_like(got)
+    assert ops.attn_latent_mma_supports(torch.bfloat16, dk, dv)
+    ops.attn_latent_mma(q, q.stride(0), got, cache_d, table_d, cu, start, work, work.shape[0], heads, dk, dv, scale)
+    ops.attn_latent_mma(q, q.stride(0), got, cache_d, table_d, cu, start, dwork, 1, heads, dk, dv, scale,
+                        split_size=32, n_splits=5)
+    ops.attn_simt(q, q.stride(0), want, cache_d, cache_d, table_d, cu, start, work_s, work_s.shape[0], heads, 1, dk, 0,
+                  scale, v_dim=dv)
+    ops.attn_simt(q, q.stride(0), want, cache_d, cache_d, table_d, cu, start, dwork, 1, heads, 1, dk, 0, scale,
+                  split_size=32, n_splits=5, v_dim=dv)
+    ops.check_status()
+    assert torch.isfinite(got.float()).all()
+    assert (got.float() - want.float()).abs().max() < 2e-2          # P is rounded to bfloat16 before it meets V
+
+
 # --------------------------------------------------------------- models of several sizes
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_each_request_alone_and_whole(setup, dtype, tmp_path):
