@@ -67,7 +67,10 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
   constexpr int THREADS = 128 * WD;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rw = warp & 3, dw = warp >> 2;
-  const int entry = p.work[2 * blockIdx.x], q_off = p.work[2 * blockIdx.x + 1];
+  // the work list runs from an entry's first tile to its last: taken from the back, the tiles with the most keys
+  // start first and the short ones fill the end of the launch
+  const int item = SPLIT ? blockIdx.x : gridDim.x - 1 - blockIdx.x;
+  const int entry = p.work[2 * item], q_off = p.work[2 * item + 1];
   const int hg = blockIdx.y;
   const int q_begin = p.cu_seqlens[entry];
   const int q_len = p.cu_seqlens[entry + 1] - q_begin;
@@ -145,21 +148,37 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
     const __nv_bfloat16* Kc = Ks + (size_t)buf * BLOCK_N * ks;
 
     // ---- scores of this warp's 16 rows against the chunk's 32 keys
-    float s[4][4];
+    // two sets of accumulators take the k steps in turn (eight independent products in flight a warp), added at the end
+    float s[4][4], s2[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-      for (int k = 0; k < 4; ++k) s[i][k] = 0.f;
-    for (int kk = 0; kk < dkp; kk += 16) {
+      for (int k = 0; k < 4; ++k) s[i][k] = s2[i][k] = 0.f;
+    const __nv_bfloat16* qa = Qs + (rw * 16 + (lane & 15)) * qs + (lane >> 4) * 8;
+    const __nv_bfloat16* kb = Kc + ((lane & 7) + (lane >> 4) * 8) * ks + ((lane >> 3) & 1) * 8;
+    for (int kk = 0; kk < dkp; kk += 32) {
       uint32_t a[4], b01[4], b23[4];
-      ldsm_x4(a, Qs + (rw * 16 + (lane & 15)) * qs + kk + (lane >> 4) * 8);
-      ldsm_x4(b01, Kc + ((lane & 7) + (lane >> 4) * 8) * ks + kk + ((lane >> 3) & 1) * 8);
-      ldsm_x4(b23, Kc + (16 + (lane & 7) + (lane >> 4) * 8) * ks + kk + ((lane >> 3) & 1) * 8);
+      ldsm_x4(a, qa + kk);
+      ldsm_x4(b01, kb + kk);
+      ldsm_x4(b23, kb + 16 * ks + kk);
       mma_bf16(s[0], a, b01[0], b01[1]);
       mma_bf16(s[1], a, b01[2], b01[3]);
       mma_bf16(s[2], a, b23[0], b23[1]);
       mma_bf16(s[3], a, b23[2], b23[3]);
+      if (kk + 16 < dkp) {
+        ldsm_x4(a, qa + kk + 16);
+        ldsm_x4(b01, kb + kk + 16);
+        ldsm_x4(b23, kb + 16 * ks + kk + 16);
+        mma_bf16(s2[0], a, b01[0], b01[1]);
+        mma_bf16(s2[1], a, b01[2], b01[3]);
+        mma_bf16(s2[2], a, b23[0], b23[1]);
+        mma_bf16(s2[3], a, b23[2], b23[3]);
+      }
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) s[i][k] += s2[i][k];
     // ---- mask, running softmax (32-bit)
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -226,7 +245,7 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
     const float l = half ? l1 : l0, mm = half ? m1 : m0;
     size_t slot = 0;
     if (SPLIT) {
-      slot = ((size_t)blockIdx.x * p.n_heads + head) * p.n_splits + blockIdx.z;
+      slot = ((size_t)item * p.n_heads + head) * p.n_splits + blockIdx.z;
       if (dw == 0 && (lane & 3) == 0) { p.part_ml[slot * 2] = mm; p.part_ml[slot * 2 + 1] = l; }
     }
     const float inv = 1.f / l;
