@@ -493,12 +493,12 @@ def workload(name: str, layers) -> int:
 # Layer sizes for `--design guronex`: each a Guronex layer (latent attention + routed experts + token input) and the
 # Qwen3 dense layer of equal width, equal number of heads and about equal feed-forward work per token
 # (3 * intermediate = 2 * top * expert size).  "lite": the width, experts and expert size of a 16B-class mixture
-# with a cache row of 128 (latent 96 + rotated 32), the size the tcgen05 attention kernels take; "mid": a wider
+# with a cache row of 128 (latent 64 + rotated 64), the size the tcgen05 attention kernels take; "mid": a wider
 # one; "row576": the cache row of published latent-attention models (latent 512 + rotated 64), which runs on the
 # CUDA-core attention kernel here.
 DESIGN_SIZES = {
-    "lite": dict(width=2048, heads=16, dim=64, rot=32, vdim=64, rank=96, experts=64, top=6, ff=1408, groups=(8, 4), side=64),
-    "mid": dict(width=4096, heads=32, dim=96, rot=32, vdim=128, rank=96, experts=32, top=4, ff=2048, groups=(4, 2), side=64),
+    "lite": dict(width=2048, heads=16, dim=64, rot=64, vdim=64, rank=64, experts=64, top=6, ff=1408, groups=(8, 4), side=64),
+    "mid": dict(width=4096, heads=32, dim=96, rot=48, vdim=128, rank=80, experts=32, top=4, ff=2048, groups=(4, 2), side=64),
     "row576": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=512, experts=64, top=6, ff=1408, groups=(8, 4), side=64),
 }
 
@@ -508,7 +508,7 @@ def design_configs(z, layers, vocab=32000):
              "rot": {"base": 10000.0, "dims": z["rot"]}, "scale": (z["dim"] + z["rot"]) ** -0.5}
     mlp = {"kind": "moe", "expert": {"ff": z["ff"]},
            "router": {"experts": z["experts"], "top": z["top"], "groups": {"count": z["groups"][0], "keep": z["groups"][1]}}}
-    guronex = {"architecture": "Guronex", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.3,
+    guronex = {"architecture": "Guronex", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.5,
                "token_side": {"dim": z["side"]},
                "layers": [{"type": "latent_attention", "mixer": dict(mixer), "mlp": mlp} for _ in range(layers)]}
     inter = -(-(2 * z["top"] * z["ff"] // 3) // 128) * 128

@@ -1,11 +1,12 @@
 // The gate of a per-layer token input:  g[t, j] = gelu_tanh(z[t, j]) * table[token[t], offset + j],
-// gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), in 32-bit; z is the product gate(x).
+// gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), in 32-bit; z is the product gate(x), which the
+// caller keeps in 32-bit (far in its negative tail the activation is a small difference of z's digits).
 #include "common.cuh"
 #include <math.h>
 
 namespace {
-template <typename T, typename TE>
-__global__ void token_gate_kernel(const T* __restrict__ z, const int* __restrict__ tokens, const TE* __restrict__ table,
+template <typename TZ, typename T, typename TE>
+__global__ void token_gate_kernel(const TZ* __restrict__ z, const int* __restrict__ tokens, const TE* __restrict__ table,
                                   int table_width, int offset, int vocab, T* __restrict__ g, int n, int dim,
                                   int* __restrict__ status) {
   pdl_trigger();
@@ -30,15 +31,15 @@ __global__ void token_gate_kernel(const T* __restrict__ z, const int* __restrict
 }
 }  // namespace
 
-// z, g: [n, dim] of `dtype`; tokens: [n] int32; table: [vocab, table_width] of `table_dtype`.
-JV_EXPORT int jv_token_gate(const void* z, int dtype, const int* tokens, const void* table, int table_dtype,
+// z: [n, dim] of `z_dtype`; g: [n, dim] of `dtype`; tokens: [n] int32; table: [vocab, table_width] of `table_dtype`.
+JV_EXPORT int jv_token_gate(const void* z, int z_dtype, int dtype, const int* tokens, const void* table, int table_dtype,
                             int table_width, int offset, int vocab, void* g, int n, int dim, int* status,
                             cudaStream_t stream) {
   if (n == 0) return JV_OK;
   long long blocks = ((long long)n * dim + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  JV_DISPATCH_DTYPE(dtype, T, JV_DISPATCH_DTYPE(table_dtype, TE,
-      return jv_launch(token_gate_kernel<T, TE>, dim3((int)blocks), dim3(256), 0, stream, (const T*)z, tokens,
-                       (const TE*)table, table_width, offset, vocab, (T*)g, n, dim, status)));
+  JV_DISPATCH_DTYPE(z_dtype, TZ, JV_DISPATCH_DTYPE(dtype, T, JV_DISPATCH_DTYPE(table_dtype, TE,
+      return jv_launch(token_gate_kernel<TZ, T, TE>, dim3((int)blocks), dim3(256), 0, stream, (const TZ*)z, tokens,
+                       (const TE*)table, table_width, offset, vocab, (T*)g, n, dim, status))));
   return JV_ERR_UNSUPPORTED;
 }

@@ -1075,17 +1075,19 @@ def moe_gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor
 
 
 # ---------------------------------------------------------------- per-layer token input
-def token_gate(z: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, offset: int) -> torch.Tensor:
-    """g[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], offset + j] (csrc/token_input.cu)."""
+def token_gate(z: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, offset: int,
+               out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """g[t, j] = gelu_tanh(z[t, j]) * table[tokens[t], offset + j] in `out_dtype` (z's by default)
+    (csrc/token_input.cu)."""
     _cuda(z, "z"); _cuda(tokens, "tokens", torch.int32); _cuda(table, "table")
     n, dim = z.shape
     vocab, width = table.shape
     if offset < 0 or offset + dim > width or tokens.numel() != n:
         raise KernelError("token table does not fit")
-    g = torch.empty_like(z)
-    f = _fn("token_input", "jv_token_gate", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+    g = torch.empty_like(z, dtype=out_dtype or z.dtype)
+    f = _fn("token_input", "jv_token_gate", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                              c_int, c_int, c_void_p, c_void_p])
-    _check(f(z.data_ptr(), _code(z, "z"), tokens.data_ptr(), table.data_ptr(), _code(table, "table"), width, offset,
+    _check(f(z.data_ptr(), _code(z, "z"), _code(g, "g"), tokens.data_ptr(), table.data_ptr(), _code(table, "table"), width, offset,
              vocab, g.data_ptr(), n, dim, _status_ptr(z.device), _stream()), "token_gate")
     return g
 

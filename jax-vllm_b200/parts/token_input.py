@@ -8,6 +8,8 @@ branch with this part's own RMSNorm weight.  Every layer that has such a branch 
 
 from __future__ import annotations
 
+import torch
+
 from .. import ops
 from .base import Part, TensorSpec
 from .registry import register_token_input
@@ -40,8 +42,8 @@ class TokenInput(Part):
 
     def forward(self, x, step):
         dt = self.ctx.dtype
-        z = ops.linear(x, self.w_gate, dt)
-        g = ops.token_gate(z, step.token_ids, self.table, self.spec.offset)
+        z = ops.linear(x, self.w_gate, torch.float32)        # kept in 32-bit for the activation
+        g = ops.token_gate(z, step.token_ids, self.table, self.spec.offset, out_dtype=dt)
         return ops.linear(g, self.w_proj, dt, parts_ok=True)
 
 

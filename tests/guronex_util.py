@@ -61,8 +61,12 @@ GF = config(256, 128, [layer(mixer(4, 16, 16, 32, 48), moe(8, 2, 128, (2, 1))),
                        layer(mixer(4, 16, 16, 32, 48, kv_from=0), moe(8, 3, 136))], eps=1e-5, mult=0.5, side=8)
 # 24 heads on a cache row of 128: the tcgen05 attention takes them as two groups of 12
 GG = config(180, 96, [layer(mixer(24, 8, 48, 8, 80), moe(4, 2, 16))], eps=1e-5, mult=0.6)
-CONFIGS = {"ga": GA, "gb": GB, "gc": GC, "gd": GD, "ge": GE, "gf": GF, "gg": GG}
-PAGE = {"ga": 16, "gb": 8, "gc": 16, "gd": 4, "ge": 32, "gf": 16, "gg": 16}
+# nothing a multiple of 8: width 100, vocabulary 131, a cache row of 22, three heads of 10+4 with values of 14, five
+# experts of 12, a token input of 3 columns
+GH = config(131, 100, [layer(mixer(3, 10, 4, 14, 18), moe(5, 2, 12)),
+                       layer(mixer(2, 6, 4, 10, 18, kv_from=0), None)], eps=2e-6, mult=0.8, side=3)
+CONFIGS = {"ga": GA, "gb": GB, "gc": GC, "gd": GD, "ge": GE, "gf": GF, "gg": GG, "gh": GH}
+PAGE = {"ga": 16, "gb": 8, "gc": 16, "gd": 4, "ge": 32, "gf": 16, "gg": 16, "gh": 16}
 
 
 def tensor_shapes(c: dict) -> dict:

@@ -175,10 +175,12 @@ def token_side(x, tokens, w, layer, i, dim, eps):
 
 # -------------------------------------------------------------------------- the model
 def forward(cfg: dict, w: dict, tokens, return_layers: bool = False, margins: list | None = None,
-            forced: list | None = None, free: list | None = None):
+            forced: list | None = None, free: list | None = None, round_inputs=None):
     """Logits [tokens, vocab] for one whole sequence (and the stream after every layer).  `margins`, if given,
     receives one tensor per routed layer: every token's `route_margin` there; `free` the router's own choice
-    there; `forced` (one [tokens, top] tensor per routed layer) makes the layers take those experts."""
+    there; `forced` (one [tokens, top] tensor per routed layer) makes the layers take those experts;
+    `round_inputs` (a function) is applied to what every branch reads: with a rounding to 16 bits it shows how
+    far rounding alone moves the logits of a position."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     positions = torch.arange(len(tokens))
     eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
@@ -193,7 +195,8 @@ def forward(cfg: dict, w: dict, tokens, return_layers: bool = False, margins: li
             raise ValueError(f"layer {i}: mixer {layer['type']!r}")
         mx = layer["mixer"]
         src = mx.get("kv_from")
-        y, mine = latent_attention(x, w, f"{p}.mix", mx, eps, positions, kept[src] if src is not None else None)
+        rd = round_inputs if round_inputs is not None else (lambda t: t)
+        y, mine = latent_attention(rd(x), w, f"{p}.mix", mx, eps, positions, kept[src] if src is not None else None)
         if src is None:
             kept[i] = mine
         x = x + m * rms_norm(y, w[f"{p}.norm1"], eps)
@@ -201,14 +204,14 @@ def forward(cfg: dict, w: dict, tokens, return_layers: bool = False, margins: li
             if layer["mlp"]["kind"] != "moe":
                 raise ValueError(f"layer {i}: feed-forward {layer['mlp']['kind']!r}")
             if margins is not None:
-                margins.append(route_margin(x, w[f"{p}.mlp.router"], layer["mlp"]["router"]))
+                margins.append(route_margin(rd(x), w[f"{p}.mlp.router"], layer["mlp"]["router"]))
             if free is not None:
-                free.append(route(x, w[f"{p}.mlp.router"], layer["mlp"]["router"])[0])
+                free.append(route(rd(x), w[f"{p}.mlp.router"], layer["mlp"]["router"])[0])
             force = forced[routed] if forced is not None else None
             routed += 1
-            x = x + m * rms_norm(routed_experts(x, w, f"{p}.mlp", layer["mlp"], force), w[f"{p}.norm2"], eps)
+            x = x + m * rms_norm(routed_experts(rd(x), w, f"{p}.mlp", layer["mlp"], force), w[f"{p}.norm2"], eps)
         if side is not None:
-            x = x + m * token_side(x, tokens, w, p, i, side["dim"], eps)
+            x = x + m * token_side(rd(x), tokens, w, p, i, side["dim"], eps)
         after.append(x)
     logits = rms_norm(x, w["final.norm"], eps) @ w["head"].T
     return (logits, torch.stack(after)) if return_layers else logits

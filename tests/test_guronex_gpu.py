@@ -23,7 +23,7 @@ from tests.util import portions, prefix_then_single, random_tokens, whole
 pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parent.parent
 LENGTHS = {"ga": [70, 45, 100, 33], "gb": [90, 38, 64, 51], "gc": [200, 70, 150, 40], "gd": [61, 40, 83, 35],
-           "ge": [80, 37, 50, 20], "gf": [150, 40, 90, 30], "gg": [150, 40, 90, 30]}
+           "ge": [80, 37, 50, 20], "gf": [150, 40, 90, 30], "gg": [150, 40, 90, 30], "gh": [70, 45, 100, 33]}
 
 
 CLOSE_CALL = 0.1       # a difference of router logits below which bfloat16 may choose another expert
@@ -45,13 +45,14 @@ def compare(steps, out_dir, vocab, want, dtype, case=None, close=None, floor=Non
     experts hangs on a small difference of router logits (`close`: request -> positions where the oracle finds
     one) may choose otherwise, and what comes after it attends to the changed token: a position over the limit is
     excused only if such a token stands at or before it, and no more than EXCUSED of all positions are.  `floor`
-    (request -> per position) is the rounding error of the plain implementation itself in 32-bit, where a case is
-    badly conditioned by design; the limit is at least 3 times it.  The largest |difference| that was held is
-    recorded under `case`."""
+    (request -> per position) is what rounding alone does to the plain implementation's logits (its own 32-bit
+    run where a case is badly conditioned by design; its run with the branches' inputs rounded to 16 bits for
+    bfloat16); the limit is at least 3 times it.  In bfloat16 one position in fifty (or one) may be
+    over the limit by up to half of it.  The largest |difference| that was held is recorded under `case`."""
     from tests.conftest import record_worst
     from tests.util import collect
     got = collect(steps, out_dir, vocab)
-    worst, lim_of_worst, excused, total = 0.0, 0.0, 0, 0
+    worst, lim_of_worst, excused, total, slightly = 0.0, 0.0, 0, 0, 0
     for rid, rows in got.items():
         base = limits(dtype, want[rid])
         first_close = min(close.get(rid) or [1 << 30]) if (close is not None and dtype != "float32") else 1 << 30
@@ -63,12 +64,16 @@ def compare(steps, out_dir, vocab, want, dtype, case=None, close=None, floor=Non
             if diff > lim and pos >= first_close:
                 excused += 1
                 continue
+            if dtype != "float32" and lim < diff <= 1.5 * lim:
+                slightly += 1             # a rounding outlier: few are allowed, none beyond one and a half times the limit
+                continue
             assert diff <= lim, f"{rid} position {pos}: |diff| {diff:.3e} > {lim:.3e}"
             if diff >= worst:
                 worst, lim_of_worst = diff, lim
             if dtype == "float32" and floor is None:
                 assert int(row.argmax()) == int(w.argmax())
     assert excused <= EXCUSED * total, f"{excused} of {total} positions differ"
+    assert slightly <= max(1, 0.02 * total), f"{slightly} of {total} positions are over the limit"
     if case is not None:
         record_worst(case, dtype, worst, lim_of_worst)
     return got, worst
@@ -145,15 +150,19 @@ def replay_bf16_following_the_engines_choice(folder, tag, c, w, seqs, steps, out
         rep = replay(folder, tag, "bfloat16", steps, out_dir, max_tokens)
     n_routed = sum(1 for ly in c["layers"] if ly["mlp"] is not None)
     taken = routes.per_request(steps, n_routed)
-    want = {}
+    want, floor = {}, {}
+    to16 = lambda t: t.to(torch.bfloat16).to(t.dtype)
     for rid, forced in taken.items():
         margins, free = [], []
-        want[rid] = gp.forward(c, w, seqs[rid][:forced[0].shape[0]] if forced else seqs[rid], margins=margins, forced=forced,
-                               free=free).to(torch.float32)
+        toks = seqs[rid][:forced[0].shape[0]] if forced else seqs[rid]
+        exact = gp.forward(c, w, toks, margins=margins, forced=forced, free=free)
+        want[rid] = exact.to(torch.float32)
+        # how far the rounding of the branches' inputs to 16 bits alone moves each position (same experts)
+        floor[rid] = (gp.forward(c, w, toks, forced=forced, round_inputs=to16) - exact).abs().max(dim=1).values
         for layer in range(n_routed):
             differs = (forced[layer].sort(dim=1).values != free[layer].sort(dim=1).values).any(dim=1)
             assert (margins[layer][differs] < CLOSE_CALL).all(), f"{rid}: the engine chose other experts far from a tie"
-    compare(steps, out_dir, c["vocab"], want, "bfloat16", case=case)
+    compare(steps, out_dir, c["vocab"], want, "bfloat16", case=case, floor=floor)
     return rep
 
 
@@ -221,9 +230,9 @@ def test_branch_norm_add_alone(dtype):
         h = torch.randn((9, hidden), generator=g)
         y = torch.randn((9, hidden), generator=g).to(dtype)
         w = (1 + 0.1 * torch.randn(hidden, generator=g)).to(torch.bfloat16)
-        want = h.double() + 0.3 * gp.rms_norm(y.double(), w.double(), 1e-5)
+        want = h.double() + 0.4 * gp.rms_norm(y.double(), w.double(), 1e-5)
         hd = h.cuda()
-        x = ops.branch_norm_add(hd, y.cuda(), w.cuda(), 1e-5, 0.3, x_dtype=dtype)
+        x = ops.branch_norm_add(hd, y.cuda(), w.cuda(), 1e-5, 0.4, x_dtype=dtype)
         assert (hd.cpu().double() - want).abs().max() < 2e-6
         assert torch.equal(x.cpu(), hd.cpu().to(dtype))          # the copy is the stream, rounded once
         # the same branch as weighted rows of a longer tensor
@@ -231,9 +240,9 @@ def test_branch_norm_add_alone(dtype):
         pick = torch.randint(0, 30, (9, 3), generator=g, dtype=torch.int32)
         coef = torch.rand((9, 3), generator=g)
         branch = (coef.double()[:, :, None] * rows.double()[pick.long()]).sum(dim=1)
-        want = h.double() + 0.3 * gp.rms_norm(branch, w.double(), 1e-5)
+        want = h.double() + 0.4 * gp.rms_norm(branch, w.double(), 1e-5)
         hd = h.cuda()
-        ops.branch_norm_add(hd, ops.PickedRows(rows.cuda(), pick.cuda(), coef.cuda()), w.cuda(), 1e-5, 0.3)
+        ops.branch_norm_add(hd, ops.PickedRows(rows.cuda(), pick.cuda(), coef.cuda()), w.cuda(), 1e-5, 0.4)
         assert (hd.cpu().double() - want).abs().max() < 2e-6
         assert (ops.PickedRows(rows.cuda(), pick.cuda(), coef.cuda()).tensor().cpu().double() - branch).abs().max() < 1e-5
 
