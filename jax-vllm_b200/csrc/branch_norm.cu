@@ -59,6 +59,95 @@ __global__ void branch_norm_add_kernel(float* __restrict__ h, const TD* __restri
   }
 }
 
+// eight elements at a time (16 bytes of bfloat16, 32 of float)
+template <typename T> __device__ __forceinline__ void ld8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void ld8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void ld8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&a);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) { const float2 f = __bfloat1622float2(h[k]); v[2 * k] = f.x; v[2 * k + 1] = f.y; }
+}
+template <typename T> __device__ __forceinline__ void st8(T* p, const float (&v)[8]);
+template <> __device__ __forceinline__ void st8<float>(float* p, const float (&v)[8]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <> __device__ __forceinline__ void st8<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[8]) {
+  uint4 a;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&a);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+  *reinterpret_cast<uint4*>(p) = a;
+}
+
+// The same as branch_norm_add_kernel with eight elements a thread and pass (hidden a multiple of 8, every pointer
+// 16-byte aligned): the sums are formed in the same order, element by element, so the results are the same bits.
+template <typename TD, typename TW, typename TX>
+__global__ void branch_norm_add_vec_kernel(float* __restrict__ h, const TD* __restrict__ y, size_t part_stride, int parts,
+                                           const int* __restrict__ pick, const float* __restrict__ coef, int y_rows,
+                                           const TW* __restrict__ weight, TX* __restrict__ x_out, int hidden, float eps,
+                                           float mult, int* __restrict__ status) {
+  extern __shared__ float row[];
+  __shared__ float scratch[33];
+  __shared__ int pick_s[MAX_PICKS];
+  __shared__ float coef_s[MAX_PICKS];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  if (pick != nullptr) {
+    if (threadIdx.x < parts) {
+      int src = pick[(size_t)r * parts + threadIdx.x];
+      if (src < 0 || src >= y_rows) { atomicOr(status, JV_STATUS_BAD_ROW); src = -1; }
+      pick_s[threadIdx.x] = src;
+      coef_s[threadIdx.x] = coef[(size_t)r * parts + threadIdx.x];
+    }
+    __syncthreads();
+  }
+  float ss = 0.f;
+  for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+    float v[8];
+    if (pick != nullptr) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[k] = 0.f;
+      for (int s = 0; s < parts; ++s)
+        if (pick_s[s] >= 0) {
+          float t[8];
+          ld8<TD>(y + (size_t)pick_s[s] * hidden + c, t);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) v[k] = fmaf(coef_s[s], t[k], v[k]);
+        }
+    } else {
+      ld8<TD>(y + (size_t)r * hidden + c, v);
+      for (int s = 1; s < parts; ++s) {
+        float t[8];
+        ld8<TD>(y + s * part_stride + (size_t)r * hidden + c, t);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] += t[k];
+      }
+    }
+    st8<float>(row + c, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += v[k] * v[k];
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = mult * rsqrtf(ss / (float)hidden + eps);
+  float* hr = h + (size_t)r * hidden;
+  for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+    float a[8], b[8], w[8];
+    ld8<float>(hr + c, a);
+    ld8<float>(row + c, b);
+    ld8<TW>(weight + c, w);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) a[k] = a[k] + b[k] * inv * w[k];
+    st8<float>(hr + c, a);
+    if (x_out != nullptr) st8<TX>(x_out + (size_t)r * hidden + c, a);
+  }
+}
+
 template <typename TD>
 __global__ void pick_rows_sum_kernel(const TD* __restrict__ y, const int* __restrict__ pick, const float* __restrict__ coef,
                                      int parts, int y_rows, float* __restrict__ out, int hidden, int* __restrict__ status) {
@@ -101,13 +190,22 @@ JV_EXPORT int jv_branch_norm_add(float* h, const void* y, int y_dtype, long long
   int threads = 64;
   while (threads < 512 && threads * 4 < hidden) threads *= 2;
   const size_t smem = (size_t)hidden * sizeof(float);
+  const bool vec = hidden % 8 == 0 && part_stride % 8 == 0 && ((uintptr_t)h % 16) == 0 && ((uintptr_t)y % 16) == 0 &&
+                   ((uintptr_t)weight % 16) == 0 && ((uintptr_t)x_out % 16) == 0;
+  if (vec) {
+    threads = 32;
+    while (threads < 256 && threads * 8 < hidden) threads *= 2;
+  }
   JV_DISPATCH_DTYPE(y_dtype, TD, JV_DISPATCH_DTYPE(weight_dtype, TW, JV_DISPATCH_DTYPE(x_dtype, TX, {
-    auto kern = branch_norm_add_kernel<TD, TW, TX>;
-    static size_t allowed = 48 * 1024;
-    if (smem > allowed) {
-      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-        return JV_ERR_UNSUPPORTED;
-      allowed = smem;
+    auto kern = vec ? branch_norm_add_vec_kernel<TD, TW, TX> : branch_norm_add_kernel<TD, TW, TX>;
+    if (smem > 48 * 1024) {       // rows beyond 12,288 elements: both forms are allowed the larger size once
+      static size_t allowed = 0;
+      if (smem > allowed) {
+        if (cudaFuncSetAttribute(branch_norm_add_vec_kernel<TD, TW, TX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+            cudaFuncSetAttribute(branch_norm_add_kernel<TD, TW, TX>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+          return JV_ERR_UNSUPPORTED;
+        allowed = smem;
+      }
     }
     return jv_launch(kern, dim3(n), dim3(threads), smem, stream, h, (const TD*)y, (size_t)part_stride, parts, pick,
                      coef, y_rows, (const TW*)weight, (TX*)x_out, hidden, eps, mult, status);

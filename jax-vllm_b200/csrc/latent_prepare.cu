@@ -56,9 +56,19 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const PrepareParams
   }
   if (p.q_latent != nullptr) {
     const T* ql = (const T*)p.q_latent;
-    for (int idx = tid; idx < p.heads * p.latent_dim; idx += blockDim.x) {
-      const int hh = idx / p.latent_dim, i = idx - hh * p.latent_dim;
-      qo[(size_t)hh * dk + i] = ql[((size_t)hh * p.n + t) * p.latent_dim + i];
+    constexpr int V = 16 / sizeof(T);             // elements in 16 bytes
+    if (p.latent_dim % V == 0 && dk % V == 0 && p.q_out_stride % V == 0 && ((uintptr_t)ql % 16) == 0 && ((uintptr_t)p.q_out % 16) == 0) {
+      const int per = p.latent_dim / V;
+      for (int idx = tid; idx < p.heads * per; idx += blockDim.x) {
+        const int hh = idx / per, i = (idx - hh * per) * V;
+        *reinterpret_cast<uint4*>(qo + (size_t)hh * dk + i) =
+            *reinterpret_cast<const uint4*>(ql + ((size_t)hh * p.n + t) * p.latent_dim + i);
+      }
+    } else {
+      for (int idx = tid; idx < p.heads * p.latent_dim; idx += blockDim.x) {
+        const int hh = idx / p.latent_dim, i = idx - hh * p.latent_dim;
+        qo[(size_t)hh * dk + i] = ql[((size_t)hh * p.n + t) * p.latent_dim + i];
+      }
     }
   }
   if (p.cache == nullptr) return;
@@ -88,6 +98,34 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(const PrepareParams
     }
     dst[p.latent_dim + i] = from_f32<T>(u);
     dst[p.latent_dim + i + half] = from_f32<T>(v);
+  }
+}
+
+// eight bfloat16 elements a thread (dv a multiple of 8, 16-byte aligned rows)
+__global__ void gate_heads_vec_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ g, int g_stride,
+                                      __nv_bfloat16* __restrict__ out, int n, int heads, int dv) {
+  pdl_trigger();
+  pdl_wait();
+  const int per = dv / 8;
+  const size_t total = (size_t)n * heads * per;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const int d = (int)(i % per) * 8;
+    const int hh = (int)((i / per) % heads);
+    const size_t t = i / ((size_t)per * heads);
+    uint4 a = *reinterpret_cast<const uint4*>(o + ((size_t)hh * n + t) * dv + d);
+    if (g != nullptr) {
+      const uint4 b = *reinterpret_cast<const uint4*>(g + t * g_stride + (size_t)hh * dv + d);
+      __nv_bfloat162* ah = reinterpret_cast<__nv_bfloat162*>(&a);
+      const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 x = __bfloat1622float2(ah[k]), y = __bfloat1622float2(bh[k]);
+        ah[k] = __floats2bfloat162_rn(x.x * (1.f / (1.f + expf(-y.x))), x.y * (1.f / (1.f + expf(-y.y))));
+      }
+    }
+    *reinterpret_cast<uint4*>(out + (t * heads + hh) * dv + d) = a;
   }
 }
 
@@ -134,6 +172,13 @@ JV_EXPORT int jv_gate_heads(const void* o, const void* g, int g_stride, void* ou
   if (n == 0) return JV_OK;
   long long blocks = ((long long)n * heads * dv + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
+  if (dtype == 1 && dv % 8 == 0 && g_stride % 8 == 0 && ((uintptr_t)o % 16) == 0 && ((uintptr_t)g % 16) == 0 &&
+      ((uintptr_t)out % 16) == 0) {
+    long long vblocks = ((long long)n * heads * (dv / 8) + 255) / 256;
+    if (vblocks > 148 * 16) vblocks = 148 * 16;
+    return jv_launch(gate_heads_vec_kernel, dim3((int)vblocks), dim3(256), 0, stream, (const __nv_bfloat16*)o,
+                     (const __nv_bfloat16*)g, g_stride, (__nv_bfloat16*)out, n, heads, dv);
+  }
   JV_DISPATCH_DTYPE(dtype, T, return jv_launch(gate_heads_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
                                                (const T*)o, (const T*)g, g_stride, (T*)out, n, heads, dv));
   return JV_ERR_UNSUPPORTED;
