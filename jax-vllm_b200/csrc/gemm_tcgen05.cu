@@ -94,6 +94,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
   const int tiles_m = used_row_tiles != nullptr ? min(*used_row_tiles, (M + BM - 1) / BM) : (M + BM - 1) / BM;
   const int tiles_n = (N + BN - 1) / BN;
   const int n_tiles = tiles_m * tiles_n;
+  // grouped: the column tiles of a row tile follow one another, so that the blocks at work at one time share the row
+  // tile's rows of A, and the row tiles of one expert (neighbours) its weight tiles, through the L2
+  const bool grouped = tile_expert != nullptr;
   const int k_blocks = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -119,12 +122,13 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
       int s = 0, phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        const int mt = grouped ? tile / tiles_n : tile % tiles_m, nt = grouped ? tile % tiles_n : tile / tiles_m;
+        const int m0 = mt * BM, n0 = nt * BN;
         // grouped: the row tile belongs to one expert, whose rows of B start at expert * expert_rows; a row tile
         // without an expert is skipped (by all three roles alike)
         int b0 = n0;
         if (tile_expert != nullptr) {
-          const int e = tile_expert[tile % tiles_m];
+          const int e = tile_expert[mt];
           if (e < 0) continue;
           b0 = e * expert_rows + n0;
         }
@@ -145,7 +149,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
       int s = 0, phase = 0, it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-        if (tile_expert != nullptr && tile_expert[tile % tiles_m] < 0) continue;
+        if (tile_expert != nullptr && tile_expert[tile / tiles_n] < 0) continue;
         const int acc = it & 1, acc_phase = (it >> 1) & 1;
         ++it;
         if (!mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1)) { ok = false; break; }
@@ -172,10 +176,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_tcgen05_kernel(const __grid_c
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
-      if (tile_expert != nullptr && tile_expert[tile % tiles_m] < 0) continue;
+      if (tile_expert != nullptr && tile_expert[tile / tiles_n] < 0) continue;
       const int acc = it & 1, acc_phase = (it >> 1) & 1;
       ++it;
-      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const int m0 = (grouped ? tile / tiles_n : tile % tiles_m) * BM, n0 = (grouped ? tile % tiles_n : tile / tiles_m) * BN;
       if (!mbar_wait(&sh->acc_full[acc], acc_phase)) { ok = false; break; }
       asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
       const int row = m0 + quad * 32 + lane;
