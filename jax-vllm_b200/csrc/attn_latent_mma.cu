@@ -6,8 +6,8 @@
 // Work item = (entry, first token of the tile); grid.y = head group; grid.z = key split (1 unless SPLIT).  A tile is
 // 64 rows = (token, query head) pairs: row m -> token q_off + m / heads_per_tile, head hg * heads_per_tile +
 // m % heads_per_tile.  Warp w works on rows (w & 3) * 16 .. + 16 and, of the output columns, on the part
-// (w >> 2) * DVW .. + DVW (WD parts: a row's 512 output columns are more than one warp's registers hold; each part's
-// warp forms the scores of its rows itself).  Keys come in chunks of 32 rows by cp.async, two buffers; the chunk in
+// (w >> 2) * DVW .. + DVW (WD parts: a row's 512 output columns are more than one warp's registers hold; the two
+// warps of a row each form the scores over half of k and exchange the partial sums through shared memory).  Keys come in chunks of 32 rows by cp.async, two buffers; the chunk in
 // shared memory is the B operand of S = Q K^T as it lies (k contiguous) and, read through ldmatrix.trans, of
 // O += P V: the row is loaded once for both.  Softmax is the running (max, sum) form in registers.
 //
@@ -19,6 +19,7 @@
 
 namespace {
 constexpr int BLOCK_M = 64, BLOCK_N = 32, PAD = 8;
+constexpr int XCH_BYTES = 2 * 4 * 2 * 16 * 32 * 4;      // the exchange of partial scores between the two warps of a row
 
 struct LatentParams {
   const __nv_bfloat16* q; int q_stride;
@@ -63,6 +64,7 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);               // [BLOCK_M][qstride_s]
   __nv_bfloat16* Ks = Qs + BLOCK_M * p.qstride_s;                                // [2][BLOCK_N][kstride_s]
+  float* Xs = reinterpret_cast<float*>(Ks + 2 * BLOCK_N * p.kstride_s);          // [2][4][2][16][32], only with WD == 2
   __shared__ int row_pos_s[BLOCK_M];
   constexpr int THREADS = 128 * WD;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -84,6 +86,8 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
     if (j_lo >= j_hi) return;
   }
   const int dk = p.dk, qs = p.qstride_s, ks = p.kstride_s;
+  // scores are kept times log2(e): the softmax's exponentials are powers of two (maxima in part_ml are in that scale too)
+  const float scale_log2 = p.scale * 1.4426950408889634f;
   const int dkp = (dk + 15) & ~15;
 
   // ---- zero both key buffers once (columns that no copy writes, and rows that no key fills, must be finite)
@@ -107,20 +111,21 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
   }
   __syncthreads();
 
+  // a key row of the chunk is copied by THREADS / BLOCK_N threads, 16 bytes each a turn: one look at the block table a
+  // thread and chunk
   auto load_chunk = [&](int j0, int buf) {
-    __nv_bfloat16* dst = Ks + (size_t)buf * BLOCK_N * ks;
-    const int vecs = dk / 8;
-    for (int idx = tid; idx < BLOCK_N * vecs; idx += THREADS) {
-      const int n = idx / vecs, c8 = (idx - n * vecs) * 8;
-      const int j = j0 + n;
-      if (j >= j_hi) continue;
+    constexpr int TPR = THREADS / BLOCK_N;
+    const int n = tid / TPR, j = j0 + n;
+    if (j < j_hi) {
       const int pi = j / p.page_size;
       const int page = pi < p.table_width ? p.block_table[(size_t)entry * p.table_width + pi] : -1;
       if (page < 0 || page >= p.num_pages) {
-        if (c8 == 0) atomicOr(p.status, JV_STATUS_BAD_PAGE);
-        continue;
+        if (tid % TPR == 0) atomicOr(p.status, JV_STATUS_BAD_PAGE);
+      } else {
+        const __nv_bfloat16* src = p.cache + ((size_t)page * p.page_size + (j - pi * p.page_size)) * dk;
+        __nv_bfloat16* dst = Ks + ((size_t)buf * BLOCK_N + n) * ks;
+        for (int c8 = (tid % TPR) * 8; c8 < dk; c8 += TPR * 8) cp_async16(dst + c8, src + c8);
       }
-      cp_async16(dst + n * ks + c8, p.cache + ((size_t)page * p.page_size + (j % p.page_size)) * dk + c8);
     }
     asm volatile("cp.async.commit_group;\n" ::: "memory");
   };
@@ -148,7 +153,9 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
     const __nv_bfloat16* Kc = Ks + (size_t)buf * BLOCK_N * ks;
 
     // ---- scores of this warp's 16 rows against the chunk's 32 keys
-    // two sets of accumulators take the k steps in turn (eight independent products in flight a warp), added at the end
+    // two sets of accumulators take the k steps in turn (eight independent products in flight a warp), added at the
+    // end.  Where two warps share a row's output columns (WD == 2) each forms the scores over half of k and the two
+    // exchange their partial sums through shared memory: a + b and b + a are the same bits, so both hold the same scores.
     float s[4][4], s2[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -156,7 +163,9 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
       for (int k = 0; k < 4; ++k) s[i][k] = s2[i][k] = 0.f;
     const __nv_bfloat16* qa = Qs + (rw * 16 + (lane & 15)) * qs + (lane >> 4) * 8;
     const __nv_bfloat16* kb = Kc + ((lane & 7) + (lane >> 4) * 8) * ks + ((lane >> 3) & 1) * 8;
-    for (int kk = 0; kk < dkp; kk += 32) {
+    const int khalf = ((dkp / 16 + 1) / 2) * 16;
+    const int kbeg = WD == 2 ? dw * khalf : 0, kend = WD == 2 ? min(dkp, kbeg + khalf) : dkp;
+    for (int kk = kbeg; kk < kend; kk += 32) {
       uint32_t a[4], b01[4], b23[4];
       ldsm_x4(a, qa + kk);
       ldsm_x4(b01, kb + kk);
@@ -165,7 +174,7 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
       mma_bf16(s[1], a, b01[2], b01[3]);
       mma_bf16(s[2], a, b23[0], b23[1]);
       mma_bf16(s[3], a, b23[2], b23[3]);
-      if (kk + 16 < dkp) {
+      if (kk + 16 < kend) {
         ldsm_x4(a, qa + kk + 16);
         ldsm_x4(b01, kb + kk + 16);
         ldsm_x4(b23, kb + 16 * ks + kk + 16);
@@ -179,6 +188,21 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
     for (int i = 0; i < 4; ++i)
 #pragma unroll
       for (int k = 0; k < 4; ++k) s[i][k] += s2[i][k];
+    if (WD == 2) {
+      // [chunk parity][row warp][column half][16 values][lane]: written here, read by the partner after the pair's barrier;
+      // the buffer of this parity is written again two chunks on, after the barrier of the chunk between
+      float* mine = Xs + ((((ci & 1) * 4 + rw) * 2 + dw) * 16) * 32 + lane;
+      const float* theirs = Xs + ((((ci & 1) * 4 + rw) * 2 + (dw ^ 1)) * 16) * 32 + lane;
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mine[(i * 4 + k) * 32] = s[i][k];
+      asm volatile("bar.sync %0, 64;\n" ::"r"(1 + rw) : "memory");
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) s[i][k] += theirs[(i * 4 + k) * 32];
+    }
     // ---- mask, running softmax (32-bit)
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -188,7 +212,7 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
         const int j = j0 + i * 8 + (lane & 3) * 2 + (k & 1);
         const int pos = (k < 2) ? pos0 : pos1;
         const bool vis = pos >= 0 && j < j_hi && j <= pos;
-        s[i][k] = vis ? s[i][k] * p.scale : -INFINITY;
+        s[i][k] = vis ? s[i][k] * scale_log2 : -INFINITY;
       }
       mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
       mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
@@ -196,15 +220,15 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-    const float al0 = (m0 == -INFINITY) ? 0.f : expf(m0 - mn0), al1 = (m1 == -INFINITY) ? 0.f : expf(m1 - mn1);
+    const float al0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - mn0), al1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - mn1);
     m0 = mn0; m1 = mn1;
     float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      s[i][0] = (mn0 == -INFINITY) ? 0.f : expf(s[i][0] - mn0);
-      s[i][1] = (mn0 == -INFINITY) ? 0.f : expf(s[i][1] - mn0);
-      s[i][2] = (mn1 == -INFINITY) ? 0.f : expf(s[i][2] - mn1);
-      s[i][3] = (mn1 == -INFINITY) ? 0.f : expf(s[i][3] - mn1);
+      s[i][0] = (mn0 == -INFINITY) ? 0.f : exp2f(s[i][0] - mn0);
+      s[i][1] = (mn0 == -INFINITY) ? 0.f : exp2f(s[i][1] - mn0);
+      s[i][2] = (mn1 == -INFINITY) ? 0.f : exp2f(s[i][2] - mn1);
+      s[i][3] = (mn1 == -INFINITY) ? 0.f : exp2f(s[i][3] - mn1);
       sum0 += s[i][0] + s[i][1];
       sum1 += s[i][2] + s[i][3];
     }
@@ -279,11 +303,11 @@ __global__ void latent_combine_kernel(const LatentParams p) {
   float m_all = -INFINITY;
   for (int s = 0; s <= s_last; ++s) m_all = fmaxf(m_all, p.part_ml[(base + s) * 2]);
   float l_all = 0.f;
-  for (int s = 0; s <= s_last; ++s) l_all += expf(p.part_ml[(base + s) * 2] - m_all) * p.part_ml[(base + s) * 2 + 1];
+  for (int s = 0; s <= s_last; ++s) l_all += exp2f(p.part_ml[(base + s) * 2] - m_all) * p.part_ml[(base + s) * 2 + 1];
   const size_t token = (size_t)p.cu_seqlens[entry];
   for (int d = threadIdx.x; d < p.dv; d += blockDim.x) {
     float o = 0.f;
-    for (int s = 0; s <= s_last; ++s) o += expf(p.part_ml[(base + s) * 2] - m_all) * p.part_o[(base + s) * p.dv + d];
+    for (int s = 0; s <= s_last; ++s) o += exp2f(p.part_ml[(base + s) * 2] - m_all) * p.part_o[(base + s) * p.dv + d];
     p.out[token * p.out_stride + (size_t)head * p.dv + d] = __float2bfloat16_rn(o / l_all);
   }
 }
@@ -326,7 +350,8 @@ JV_EXPORT int jv_attn_latent_mma_supports(int dk, int dv) {
   if (dk < 8 || (dk % 8) || dv < 1 || dv > dk || dv > 512) return 0;
   const int dkp = (dk + 15) & ~15;
   const int cols = out_columns_per_warp(dv) * (dv > 256 ? 2 : 1);
-  const size_t smem = sizeof(__nv_bfloat16) * ((size_t)BLOCK_M * (dkp + PAD) + 2 * (size_t)BLOCK_N * ((dkp > cols ? dkp : cols) + PAD));
+  const size_t smem = sizeof(__nv_bfloat16) * ((size_t)BLOCK_M * (dkp + PAD) + 2 * (size_t)BLOCK_N * ((dkp > cols ? dkp : cols) + PAD)) +
+                      (dv > 256 ? XCH_BYTES : 0);
   return smem <= 220 * 1024;
 }
 
@@ -355,7 +380,8 @@ JV_EXPORT int jv_attn_latent_mma(const void* q, int q_stride, void* out, int out
   const int dvw = out_columns_per_warp(dv), wd = dv > 256 ? 2 : 1;
   p.qstride_s = dkp + PAD;
   p.kstride_s = (dkp > dvw * wd ? dkp : dvw * wd) + PAD;
-  const size_t smem = sizeof(__nv_bfloat16) * ((size_t)BLOCK_M * p.qstride_s + 2 * (size_t)BLOCK_N * p.kstride_s);
+  const size_t smem = sizeof(__nv_bfloat16) * ((size_t)BLOCK_M * p.qstride_s + 2 * (size_t)BLOCK_N * p.kstride_s) +
+                      (wd == 2 ? XCH_BYTES : 0);
   dim3 grid(n_work, (n_heads + p.heads_per_tile - 1) / p.heads_per_tile, n_splits > 0 ? n_splits : 1);
   if (wd == 2) return launch<256, 2>(p, grid, smem, stream);
   switch (dvw) {

@@ -428,7 +428,7 @@ def attn_latent_mma_supports(dtype: torch.dtype, dk: int, dv: int) -> bool:
         return False
     dkp = -(-dk // 16) * 16
     cols = (32 if dv <= 32 else 64 if dv <= 64 else 128 if dv <= 128 else 256) * (2 if dv > 256 else 1)
-    return 2 * (64 * (dkp + 8) + 2 * 32 * (max(dkp, cols) + 8)) <= 220 * 1024
+    return 2 * (64 * (dkp + 8) + 2 * 32 * (max(dkp, cols) + 8)) + (32768 if dv > 256 else 0) <= 220 * 1024
 
 
 def attn_latent_mma_tokens_per_tile(n_heads: int) -> int:
