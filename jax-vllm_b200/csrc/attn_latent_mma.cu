@@ -132,6 +132,7 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
 
   const int r0 = rw * 16 + (lane >> 2), r1 = r0 + 8;       // the two rows this thread holds parts of
   const int pos0 = row_pos_s[r0], pos1 = row_pos_s[r1];
+  const bool warp_has_rows = __any_sync(0xffffffffu, pos0 >= 0 || pos1 >= 0);
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   float o[DVW / 8][4];
 #pragma unroll
@@ -151,6 +152,10 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
     }
     __syncthreads();
     const __nv_bfloat16* Kc = Ks + (size_t)buf * BLOCK_N * ks;
+    if (!warp_has_rows) {      // none of this warp's 16 rows holds a (token, head): it only helps copying (both warps of a
+      __syncthreads();         // row skip alike, so nobody waits at their barrier)
+      continue;
+    }
 
     // ---- scores of this warp's 16 rows against the chunk's 32 keys
     // two sets of accumulators take the k steps in turn (eight independent products in flight a warp), added at the
@@ -289,8 +294,13 @@ __global__ void __launch_bounds__(128 * WD, 1) attn_latent_mma_kernel(const Late
   }
 }
 
-// Merges the key splits of single-token rows, ascending.  grid = (n_work, n_heads).
-__global__ void latent_combine_kernel(const LatentParams p) {
+// Merges the key splits of single-token rows, ascending.  grid = (n_work, n_heads), 128 threads: the splits'
+// weights 2^(m_s - m) are formed once into shared memory, then every thread adds up its columns.
+constexpr int COMBINE_MAX_SPLITS = 1024;
+
+__global__ void __launch_bounds__(128) latent_combine_kernel(const LatentParams p) {
+  __shared__ float w_s[COMBINE_MAX_SPLITS];
+  __shared__ float l_s;
   const int x = blockIdx.x, head = blockIdx.y;
   const int entry = p.work[2 * x];
   const int pos = p.start_pos[entry];
@@ -300,15 +310,28 @@ __global__ void latent_combine_kernel(const LatentParams p) {
     s_last = p.n_splits - 1;
   }
   const size_t base = ((size_t)x * p.n_heads + head) * p.n_splits;
-  float m_all = -INFINITY;
-  for (int s = 0; s <= s_last; ++s) m_all = fmaxf(m_all, p.part_ml[(base + s) * 2]);
-  float l_all = 0.f;
-  for (int s = 0; s <= s_last; ++s) l_all += exp2f(p.part_ml[(base + s) * 2] - m_all) * p.part_ml[(base + s) * 2 + 1];
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float m_all = -INFINITY;
+    for (int s = lane; s <= s_last; s += 32) m_all = fmaxf(m_all, p.part_ml[(base + s) * 2]);
+    m_all = warp_max(m_all);
+    float l = 0.f;
+    for (int s = lane; s <= s_last; s += 32) {
+      const float w = exp2f(p.part_ml[(base + s) * 2] - m_all);
+      w_s[s] = w;
+      l += w * p.part_ml[(base + s) * 2 + 1];
+    }
+    l = warp_sum(l);
+    if (lane == 0) l_s = l;
+  }
+  __syncthreads();
+  const float inv = 1.f / l_s;
   const size_t token = (size_t)p.cu_seqlens[entry];
+  __nv_bfloat16* dst = p.out + token * p.out_stride + (size_t)head * p.dv;
   for (int d = threadIdx.x; d < p.dv; d += blockDim.x) {
     float o = 0.f;
-    for (int s = 0; s <= s_last; ++s) o += exp2f(p.part_ml[(base + s) * 2] - m_all) * p.part_o[(base + s) * p.dv + d];
-    p.out[token * p.out_stride + (size_t)head * p.dv + d] = __float2bfloat16_rn(o / l_all);
+    for (int s = 0; s <= s_last; ++s) o = fmaf(w_s[s], p.part_o[(base + s) * p.dv + d], o);
+    dst[d] = __float2bfloat16_rn(o * inv);
   }
 }
 
@@ -324,7 +347,7 @@ int launch(const LatentParams& p, dim3 grid, size_t smem, cudaStream_t stream) {
     kern<<<grid, 128 * WD, smem, stream>>>(p);
     int rc = jv_check_launch();
     if (rc != JV_OK) return rc;
-    latent_combine_kernel<<<dim3(grid.x, p.n_heads), 64, 0, stream>>>(p);
+    latent_combine_kernel<<<dim3(grid.x, p.n_heads), 128, 0, stream>>>(p);
     return jv_check_launch();
   }
   auto kern = attn_latent_mma_kernel<DVW, WD, false>;
@@ -365,7 +388,7 @@ JV_EXPORT int jv_attn_latent_mma(const void* q, int q_stride, void* out, int out
                                  int page_size, int num_pages, float scale, int split_size, int n_splits, int* status,
                                  cudaStream_t stream) {
   if (n_work == 0) return JV_OK;
-  if (!jv_attn_latent_mma_supports(dk, dv) || n_heads < 1 || (q_stride % 8) || ((uintptr_t)q % 16) || ((uintptr_t)cache % 16))
+  if (!jv_attn_latent_mma_supports(dk, dv) || n_heads < 1 || n_splits > COMBINE_MAX_SPLITS || (q_stride % 8) || ((uintptr_t)q % 16) || ((uintptr_t)cache % 16))
     return JV_ERR_UNSUPPORTED;
   LatentParams p;
   p.q = (const __nv_bfloat16*)q; p.q_stride = q_stride; p.out = (__nv_bfloat16*)out; p.out_stride = out_stride;

@@ -157,7 +157,11 @@ class LatentAttention(Part):
                 ops.attn_latent_mma(q, q.stride(0), out, *args, work, n_work, H, dk, self.dc, self.spec.scale)
             dwork, n_dec = step.decode_work
             if n_dec:
-                split = self.ctx.decode_split_size
+                # keys in splits of 32 to decode_split_size positions, so short that the blocks about fill the device
+                # (one block a multiprocessor); the merge adds a request's splits in ascending order
+                want = -(-step.max_seq_len * n_dec // ops.multiprocessors(q.device))
+                split = min(self.ctx.decode_split_size, max(32, -(-want // 32) * 32))
+                split = max(split, -(-step.max_seq_len // (32 * 1024)) * 32)        # the merge takes up to 1,024 splits
                 ops.attn_latent_mma(q, q.stride(0), out, *args, dwork, n_dec, H, dk, self.dc, self.spec.scale,
                                     split_size=split, n_splits=max(1, -(-step.max_seq_len // split)))
             return out.view(n, H, self.dc)
