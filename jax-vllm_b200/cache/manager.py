@@ -39,8 +39,10 @@ class CacheGroup:
     v: Optional[torch.Tensor] = None
 
     def bytes_per_page(self, page_size: int, itemsize: int) -> int:
-        tensors = 1 if self.need.shared_kv else 2
-        return tensors * len(self.layers) * page_size * self.need.num_kv_heads * self.need.head_dim * itemsize
+        row = self.need.num_kv_heads * self.need.head_dim
+        if not self.need.shared_kv:
+            row += (self.need.v_heads or self.need.num_kv_heads) * (self.need.v_head_dim or self.need.head_dim)
+        return len(self.layers) * page_size * row * itemsize
 
 
 class PageTable:
@@ -138,7 +140,8 @@ class CacheManager:
         for g, grp in enumerate(self.groups):
             shape = (len(grp.layers), self.num_pages, self.page_size, grp.need.num_kv_heads, grp.need.head_dim)
             grp.k = torch.zeros(shape, dtype=dtype, device=device)
-            grp.v = grp.k if grp.need.shared_kv else torch.zeros(shape, dtype=dtype, device=device)
+            v_shape = shape[:3] + (grp.need.v_heads or grp.need.num_kv_heads, grp.need.v_head_dim or grp.need.head_dim)
+            grp.v = grp.k if grp.need.shared_kv else torch.zeros(v_shape, dtype=dtype, device=device)
             for i, layer in enumerate(grp.layers):
                 views[layer] = PagedLayerCache(group=g, k=grp.k[i], v=grp.v[i])
         for layer, need in self.state_layers.items():

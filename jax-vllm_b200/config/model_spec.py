@@ -28,6 +28,7 @@ class RopeSpec:
     dim: int                       # number of rotated elements of a head (<= head size, even)
     theta: float
     kind: str = "rope"
+    exact_table: bool = False      # the frequency table is formed in 64-bit and rounded once (else in 32-bit)
 
 
 @dataclass(frozen=True)
@@ -51,6 +52,55 @@ class GatedMLPSpec:
     activation: str = "silu"
     prefix: str = "mlp"
     kind: str = "gated_mlp"
+
+
+@dataclass(frozen=True)
+class TwinMapsSpec:
+    """Two score maps per head over the same values (the projections hold, head by head, [map 1 | map 2]):
+    o = a1 - lam * a2 with lam = exp(lq1 . lk1) - exp(lq2 . lk2) + offset, one number for the layer from four
+    vectors of the key size; then a weightless RMSNorm over the head's values (eps) times (1 - offset)."""
+    offset: float
+    eps: float
+    names: tuple = ("lq1", "lk1", "lq2", "lk2")
+
+
+@dataclass(frozen=True)
+class GeneralAttentionSpec:
+    """Causal grouped-query attention whose options are data: keys and values of different sizes; rotation of a
+    leading part of every head; RMSNorm over a token's WHOLE query (key) projection; values that are the keys as
+    projected; a query temperature 1 + coef * ln(floor((p + 1) / every) + 1); scores capped by tanh; softmax
+    or independent sigmoid weights with a bias per head; two score maps per head; a sigmoid output gate per head
+    or per element."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    scale: float
+    position: Optional[Any] = None         # rotation of the first position.dim elements of every head, or None
+    whole_norm_eps: Optional[float] = None  # RMSNorm over all heads of q (of k) at once, weights of that size
+    values_from_keys: bool = False          # v = k as projected (before norm and rotation); no value projection
+    query_temperature: Optional[tuple] = None   # (coef, every)
+    score_cap: Optional[float] = None       # score <- cap * tanh(score / cap)
+    weights: str = "softmax"                # "softmax", or "sigmoid": sigmoid(score + bias_h), not normalised
+    score_bias: bool = False                # a number per head added to the score (sigmoid weights)
+    twin: Optional[TwinMapsSpec] = None
+    gate: Optional[str] = None              # "head": one sigmoid gate a head; "element": one per output element
+    prefix: str = "mix"
+    # tensor names below the prefix: queries, keys, values, gate, output, whole-projection norms, score bias
+    names: tuple = ("q", "k", "v", "g", "o", "q.norm", "k.norm", "pb")
+    kind: str = "general_attention"
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec:
+    """A feed-forward without a gate: down(act(up(x)))."""
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "relu2"               # relu(z)^2
+    prefix: str = "mlp"
+    names: tuple = ("up", "down")
+    kind: str = "dense_mlp"
 
 
 @dataclass(frozen=True)
@@ -132,6 +182,9 @@ class ModelSpec:
     lm_head_name: Optional[str] = "lm_head.weight"   # None: the embedding table is the output matrix
     schedule: tuple = field(default=())
     max_position: int = 0
+    # places in the run order (indices into `run_order()`) right before which the embedding output is added to the
+    # stream once more
+    reinject: tuple = field(default=())
 
     def run_order(self) -> tuple:
         return self.schedule if self.schedule else tuple(range(len(self.layers)))
@@ -141,6 +194,9 @@ class ModelSpec:
         for i in self.run_order():
             if not 0 <= i < n:
                 raise ValueError(f"schedule names layer {i}, the model has {n}")
+        for k in self.reinject:
+            if not 0 < k < len(self.run_order()):
+                raise ValueError(f"the embedding cannot be added again before place {k} of the run order")
         for i, layer in enumerate(self.layers):
             j = layer.cache_from
             if j is not None:

@@ -126,3 +126,33 @@ JV_EXPORT int jv_swiglu(const void* gu, void* act, int dtype, int n, int inter, 
                                                 (const T*)gu, (T*)act, inter, block, total));
   return JV_ERR_UNSUPPORTED;
 }
+
+// Ungated activations of a plain feed-forward down(act(up(x))), on a column range of a wider row and into
+// a column range of a wider row (in and out may be parts of packed tensors): kind 0 = relu(z)^2.
+template <typename T>
+__global__ void unary_act_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, long long out_stride,
+                                 int cols, size_t total, int kind) {
+  pdl_trigger();
+  pdl_wait();
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total; idx += stride) {
+    const size_t n = idx / cols;
+    const int i = (int)(idx - n * cols);
+    const float z = to_f32(in[n * in_stride + i]);
+    const float r = fmaxf(z, 0.f);
+    out[n * out_stride + i] = from_f32<T>(r * r);
+  }
+}
+
+JV_EXPORT int jv_unary_act(const void* in, long long in_stride, void* out, long long out_stride, int dtype, int n, int cols,
+                           int kind, cudaStream_t stream) {
+  const size_t total = (size_t)n * cols;
+  if (total == 0) return JV_OK;
+  if (kind != 0) return JV_ERR_UNSUPPORTED;
+  size_t blocks = (total + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  JV_DISPATCH_DTYPE(dtype, T, return jv_launch(unary_act_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
+                                                (const T*)in, in_stride, (T*)out, out_stride, cols, total, kind));
+  return JV_ERR_UNSUPPORTED;
+}

@@ -34,6 +34,11 @@ struct AttnParams {
   int n_q_heads, n_kv_heads, head_dim, v_dim, page_size, num_pages, window;
   float scale;
   int tokens_per_tile, heads_per_tile, n_head_groups, split_size, n_splits;
+  int n_v_heads, v_row;      // value heads (key head kv reads value head kv % n_v_heads) and elements of a cached value row
+  float score_cap;           // > 0: score <- cap * tanh(score / cap), after the scale
+  int sigmoid;               // 1: the weight of a visible key is sigmoid(score + bias[query head]), not normalised over keys
+  const float* bias;         // [n_q_heads] or null
+  int out_f32;               // 1: `out` is float whatever the type of q and the cache
   int* status;
 };
 
@@ -41,7 +46,7 @@ template <typename T, bool SPLIT>
 __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) {
   extern __shared__ float smem[];
   const int D = p.head_dim;
-  const int DV = p.v_dim;                          // leading elements of a value row that are used (<= D)
+  const int DV = p.v_dim;                          // leading elements of a value row that are used (<= v_row)
   float* Qs = smem;                                // [BLOCK_M][D]
   float* Ks = Qs + BLOCK_M * D;                    // [BLOCK_N][D+1]
   float* Vs = Ks + BLOCK_N * (D + 1);              // [BLOCK_N][DV]
@@ -80,7 +85,8 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
     const int t = tid / p.heads_per_tile, hh = hg * p.heads_per_tile + tid % p.heads_per_tile;
     row_pos[tid] = (t < tokens_here && hh < G) ? ctx + q_off + t : -1;
     row_m[tid] = -INFINITY;
-    row_l[tid] = 0.f;
+    row_l[tid] = p.sigmoid ? 1.f : 0.f;
+    row_alpha[tid] = 1.f;
   }
   for (int idx = tid; idx < BLOCK_M * D; idx += THREADS) {
     const int m = idx / D, d = idx - m * D;
@@ -111,9 +117,9 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
         if (page < 0 || page >= p.num_pages) {
           if (lane == 0) atomicOr(p.status, JV_STATUS_BAD_PAGE);
         } else {
-          const size_t off = (((size_t)page * p.page_size + (j % p.page_size)) * p.n_kv_heads + kv_head) * D;
-          krow = kc + off;
-          vrow = vc + off;
+          const size_t slot = (size_t)page * p.page_size + (j % p.page_size);
+          krow = kc + (slot * p.n_kv_heads + kv_head) * D;
+          vrow = vc + (slot * p.n_v_heads + kv_head % p.n_v_heads) * p.v_row;
         }
       }
       for (int d = lane; d < D; d += 32) Ks[n * (D + 1) + d] = krow ? to_f32(krow[d]) : 0.f;
@@ -137,7 +143,16 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
         const int m = warp * 4 + r;
         const int pos = row_pos[m];
         const bool vis = pos >= 0 && j < j_hi && j <= pos && (p.window <= 0 || j > pos - p.window);
-        const float sc = vis ? s[r] * p.scale : -INFINITY;
+        float sc = s[r] * p.scale;
+        if (p.score_cap > 0.f) sc = p.score_cap * tanhf(sc / p.score_cap);
+        if (p.sigmoid) {
+          // ---- weights that do not depend on one another: no maximum, no sum
+          const int hh = hg * p.heads_per_tile + m % p.heads_per_tile;
+          const float b = (p.bias != nullptr && hh < G) ? p.bias[kv_head * G + hh] : 0.f;
+          Ss[m * BLOCK_N + lane] = vis ? 1.f / (1.f + expf(-(sc + b))) : 0.f;
+          continue;
+        }
+        if (!vis) sc = -INFINITY;
         // ---- running softmax for row m (this warp owns the row)
         const float m_old = row_m[m];
         const float m_new = fmaxf(m_old, warp_max(sc));
@@ -195,7 +210,9 @@ __global__ void __launch_bounds__(THREADS) attn_simt_kernel(const AttnParams p) 
           p.part_ml[slot * 2 + 1] = row_l[m];
         }
       } else {
-        ((T*)p.out)[token * p.out_stride + (size_t)head * DV + d] = from_f32<T>(acc[m][c] / row_l[m]);
+        const float o = acc[m][c] / row_l[m];
+        if (p.out_f32) ((float*)p.out)[token * p.out_stride + (size_t)head * DV + d] = o;
+        else ((T*)p.out)[token * p.out_stride + (size_t)head * DV + d] = from_f32<T>(o);
       }
     }
   }
@@ -217,6 +234,16 @@ __global__ void attn_combine_kernel(const AttnParams p) {
     s_last = p.n_splits - 1;
   }
   const size_t base = ((size_t)x * p.n_q_heads + head) * p.n_splits;
+  if (p.sigmoid) {            // un-normalised weights: the splits' sums are added, in ascending order
+    const size_t tok = (size_t)p.cu_seqlens[entry];
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+      float o = 0.f;
+      for (int s = s_first; s <= s_last; ++s) o += p.part_o[(base + s) * D + d];
+      if (p.out_f32) ((float*)p.out)[tok * p.out_stride + (size_t)head * D + d] = o;
+      else ((T*)p.out)[tok * p.out_stride + (size_t)head * D + d] = from_f32<T>(o);
+    }
+    return;
+  }
   float m_all = -INFINITY;
   for (int s = s_first; s <= s_last; ++s) m_all = fmaxf(m_all, p.part_ml[(base + s) * 2]);
   float l_all = 0.f;
@@ -227,7 +254,8 @@ __global__ void attn_combine_kernel(const AttnParams p) {
     float o = 0.f;
     for (int s = s_first; s <= s_last; ++s)
       o += expf(p.part_ml[(base + s) * 2] - m_all) * p.part_o[(base + s) * D + d];
-    ((T*)p.out)[token * p.out_stride + (size_t)head * D + d] = from_f32<T>(o / l_all);
+    if (p.out_f32) ((float*)p.out)[token * p.out_stride + (size_t)head * D + d] = o / l_all;
+    else ((T*)p.out)[token * p.out_stride + (size_t)head * D + d] = from_f32<T>(o / l_all);
   }
 }
 
@@ -250,22 +278,29 @@ JV_EXPORT int jv_attn_simt_tokens_per_tile(int n_q_heads, int n_kv_heads) {
 // [n_work, 2] int32 (entry, first token of the tile within the entry's new tokens).
 // v_dim: how many leading elements of a value row are used (0: all head_dim); out and part_o then have v_dim
 // elements per head.  A cache whose values are the leading part of its keys passes the same tensor twice.
+// jv_attn_simt_ex: keys and values of different sizes and head counts, capped scores, sigmoid weights, float output
+// (see AttnParams); jv_attn_simt is the plain softmax form with values shaped like the keys.
 // n_splits == 0: every work item attends to its whole visible range and writes `out`.
 // n_splits > 0: work items are single tokens; part_o [n_work*Hq*n_splits*D] and part_ml
 // [n_work*Hq*n_splits*2] floats are scratch; a second launch merges into `out`.
-JV_EXPORT int jv_attn_simt(const void* q, int q_stride, void* out, int out_stride, int dtype,
-                           float* part_o, float* part_ml, const void* k_cache, const void* v_cache,
-                           const int* block_table, int table_width, const int* cu_seqlens,
-                           const int* start_pos, const int* work, int n_work, int n_q_heads,
-                           int n_kv_heads, int head_dim, int page_size, int num_pages, int window,
-                           float scale, int split_size, int n_splits, int v_dim, int* status,
-                           cudaStream_t stream) {
+JV_EXPORT int jv_attn_simt_ex(const void* q, int q_stride, void* out, int out_stride, int dtype,
+                              float* part_o, float* part_ml, const void* k_cache, const void* v_cache,
+                              const int* block_table, int table_width, const int* cu_seqlens,
+                              const int* start_pos, const int* work, int n_work, int n_q_heads,
+                              int n_kv_heads, int head_dim, int page_size, int num_pages, int window,
+                              float scale, int split_size, int n_splits, int v_dim, int n_v_heads, int v_row,
+                              float score_cap, int sigmoid, const float* bias, int out_f32, int* status,
+                              cudaStream_t stream) {
   if (n_work == 0) return JV_OK;
-  if (v_dim <= 0) v_dim = head_dim;
-  if (head_dim < 1 || v_dim > head_dim || v_dim > 512 || smem_bytes(head_dim, v_dim) > 227 * 1024 || n_kv_heads < 1 ||
+  if (v_row <= 0) v_row = head_dim;
+  if (n_v_heads <= 0) n_v_heads = n_kv_heads;
+  if (v_dim <= 0) v_dim = v_row;
+  if (head_dim < 1 || v_dim > v_row || v_dim > 512 || smem_bytes(head_dim, v_dim) > 227 * 1024 || n_kv_heads < 1 ||
       n_q_heads % n_kv_heads != 0)
     return JV_ERR_UNSUPPORTED;
   AttnParams p;
+  p.n_v_heads = n_v_heads; p.v_row = v_row; p.score_cap = score_cap; p.sigmoid = sigmoid ? 1 : 0; p.bias = bias;
+  p.out_f32 = out_f32 ? 1 : 0;
   p.q = q; p.q_stride = q_stride; p.out = out; p.out_stride = out_stride;
   p.part_o = part_o; p.part_ml = part_ml; p.k_cache = k_cache; p.v_cache = v_cache;
   p.block_table = block_table; p.table_width = table_width; p.cu_seqlens = cu_seqlens;
@@ -309,4 +344,18 @@ JV_EXPORT int jv_attn_simt(const void* q, int q_stride, void* out, int out_strid
     }
   });
   return rc;
+}
+
+JV_EXPORT int jv_attn_simt(const void* q, int q_stride, void* out, int out_stride, int dtype,
+                           float* part_o, float* part_ml, const void* k_cache, const void* v_cache,
+                           const int* block_table, int table_width, const int* cu_seqlens,
+                           const int* start_pos, const int* work, int n_work, int n_q_heads,
+                           int n_kv_heads, int head_dim, int page_size, int num_pages, int window,
+                           float scale, int split_size, int n_splits, int v_dim, int* status,
+                           cudaStream_t stream) {
+  if (v_dim > head_dim) return JV_ERR_UNSUPPORTED;
+  return jv_attn_simt_ex(q, q_stride, out, out_stride, dtype, part_o, part_ml, k_cache, v_cache, block_table,
+                         table_width, cu_seqlens, start_pos, work, n_work, n_q_heads, n_kv_heads, head_dim, page_size,
+                         num_pages, window, scale, split_size, n_splits, v_dim, n_kv_heads, head_dim, 0.f, 0, nullptr,
+                         0, status, stream);
 }

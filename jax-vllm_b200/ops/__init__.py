@@ -237,16 +237,20 @@ def wait_probe(cycles: int, arrive: bool, device=None) -> tuple:
 
 
 # ------------------------------------------------------------------------ embedding
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """out[n, :] = table[ids[n], :] as float32."""
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None,
+                 accumulate: bool = False) -> torch.Tensor:
+    """out[n, :] = table[ids[n], :] as float32; with `accumulate` the rows are added to `out`."""
     _cuda(table, "table"); _cuda(ids, "ids", torch.int32)
     n, (vocab, hidden) = ids.numel(), table.shape
+    if accumulate and out is None:
+        raise KernelError("embed_gather: accumulate needs `out`")
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
     _cuda(out, "out", torch.float32)
-    f = _fn("embed", "jv_embed_gather", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    f = _fn("embed", "jv_embed_gather", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                         c_void_p])
     _check(f(table.data_ptr(), _code(table, "table"), ids.data_ptr(), out.data_ptr(), n, hidden, vocab,
-             _status_ptr(table.device), _stream()), "embed_gather")
+             1 if accumulate else 0, _status_ptr(table.device), _stream()), "embed_gather")
     return out
 
 
@@ -382,31 +386,147 @@ def attn_simt_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
 def attn_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
               block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor,
               n_work: int, n_q_heads: int, n_kv_heads: int, head_dim: int, window: int, scale: float,
-              split_size: int = 0, n_splits: int = 0, v_dim: int = 0) -> None:
+              split_size: int = 0, n_splits: int = 0, v_dim: int = 0, score_cap: float = 0.0, sigmoid: bool = False,
+              bias: torch.Tensor | None = None) -> None:
     """Paged causal attention on CUDA cores (csrc/attn_simt.cu).  `work` is [n_work, 2] int32
     (entry, first token of the tile); with `n_splits` > 0 the work items are single tokens
     whose keys are split into `n_splits` ranges of `split_size` positions.  `v_dim` > 0: only that many
     leading elements of a value row are used and `out` has v_dim elements per head (a cache whose values are
-    the leading part of its keys is passed as both caches)."""
-    for t, nm in ((q, "q"), (out, "out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
+    the leading part of its keys is passed as both caches).
+
+    The value cache may have other heads and another row size than the key cache ([pages, page, value heads,
+    value size]): key head g then reads value head g % value heads.  `score_cap` > 0 caps the scaled scores by
+    cap * tanh(score / cap); `sigmoid` replaces the softmax by independent weights sigmoid(score + bias[query
+    head]); `out` may be float32 whatever the type of q."""
+    for t, nm in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache")):
         _cuda(t, nm, q.dtype, contiguous=(nm != "q"))
+    _cuda(out, "out", contiguous=False)
+    if out.dtype not in (q.dtype, torch.float32) or out.stride(1) != 1:
+        raise KernelError("attn_simt: out must have the type of q or float32, and unit column stride")
+    if k_cache.dim() != 4 or v_cache.dim() != 4 or k_cache.shape[:2] != v_cache.shape[:2] or \
+            k_cache.shape[2:] != (n_kv_heads, head_dim) or n_kv_heads % v_cache.shape[2]:
+        raise KernelError(f"attn_simt: caches {tuple(k_cache.shape)} / {tuple(v_cache.shape)} do not fit "
+                          f"{n_kv_heads} key heads of {head_dim}")
+    n_v_heads, v_row = v_cache.shape[2], v_cache.shape[3]
+    v_dim = int(v_dim) or v_row
+    if bias is not None:
+        _cuda(bias, "bias", torch.float32)
+        if bias.numel() != n_q_heads:
+            raise KernelError("attn_simt: one bias per query head")
     for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (work, "work")):
         _cuda(t, nm, torch.int32)
     if n_work == 0:
         return
     part_o = part_ml = None
     if n_splits > 0:
-        part_o = torch.empty(n_work * n_q_heads * n_splits * (v_dim or head_dim), dtype=torch.float32, device=q.device)
+        part_o = torch.empty(n_work * n_q_heads * n_splits * v_dim, dtype=torch.float32, device=q.device)
         part_ml = torch.empty(n_work * n_q_heads * n_splits * 2, dtype=torch.float32, device=q.device)
-    f = _fn("attn_simt", "jv_attn_simt", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                          c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                          c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p,
-                                          c_void_p])
+    f = _fn("attn_simt", "jv_attn_simt_ex", [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
+                                             c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_void_p])
     _check(f(q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), _code(q, "q"), _ptr(part_o), _ptr(part_ml),
              k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1],
              cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads, n_kv_heads, head_dim,
-             k_cache.shape[1], k_cache.shape[0], int(window), float(scale), int(split_size), int(n_splits), int(v_dim),
+             k_cache.shape[1], k_cache.shape[0], int(window), float(scale), int(split_size), int(n_splits), v_dim,
+             n_v_heads, v_row, float(score_cap), 1 if sigmoid else 0, _ptr(bias), 1 if out.dtype != q.dtype else 0,
              _status_ptr(q.device), _stream()), "attn_simt", launches=2 if n_splits > 0 else 1)
+
+
+def attn_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor, positions: torch.Tensor,
+                 token_entry: torch.Tensor, block_table: torch.Tensor, inv_freq: torch.Tensor | None,
+                 q_norm_w, k_norm_w, eps: float, temp_coef: float, temp_every: int, k_cache, v_cache,
+                 n_q_heads: int, n_k_heads: int, n_v_heads: int, key_dim: int, value_dim: int) -> None:
+    """Prepares the queries, keys and values of a packed projection row for attention and writes the new keys and
+    values into the paged cache (csrc/attn_prepare.cu): RMSNorm over a token's whole query (key) projection,
+    a query temperature that grows with the position, rotation of the first `2 * len(inv_freq)` elements of every
+    head.  Offsets are columns of `proj`; `v_off` < 0: the values are the keys as projected.  Queries go to
+    `q_out` [n, n_q_heads * key_dim].  `k_cache`/`v_cache` None: queries only."""
+    _cuda(proj, "proj", contiguous=False); _cuda(q_out, "q_out", proj.dtype)
+    _cuda(positions, "positions", torch.int32); _cuda(token_entry, "token_entry", torch.int32)
+    _cuda(block_table, "block_table", torch.int32)
+    n, width = proj.shape
+    if proj.stride(1) != 1 or q_out.shape != (n, n_q_heads * key_dim):
+        raise KernelError("attn_prepare: proj needs unit column stride and q_out [n, query heads * key size]")
+    writes = k_cache is not None
+    ends = [q_off + n_q_heads * key_dim]
+    if writes:
+        ends += [k_off + n_k_heads * key_dim] + ([v_off + n_v_heads * value_dim] if v_off >= 0 else [])
+    if min(q_off, k_off if writes else 0) < 0 or max(ends) > width:
+        raise KernelError(f"attn_prepare: the heads do not fit a row of {width} columns")
+    rot_dim = 0
+    if inv_freq is not None:
+        _cuda(inv_freq, "inv_freq", torch.float32)
+        rot_dim = 2 * inv_freq.numel()
+    w_code = 0
+    for w, nm, size in ((q_norm_w, "q_norm", n_q_heads * key_dim), (k_norm_w, "k_norm", n_k_heads * key_dim)):
+        if w is not None:
+            _cuda(w, nm)
+            if w.numel() != size:
+                raise KernelError(f"{nm} weight has {w.numel()} elements, the projection {size}")
+            w_code = _code(w, nm)
+    if q_norm_w is not None and k_norm_w is not None and q_norm_w.dtype != k_norm_w.dtype:
+        raise KernelError("q_norm and k_norm weights differ in dtype")
+    page_size = num_pages = 1
+    if writes:
+        _cuda(k_cache, "k_cache", proj.dtype); _cuda(v_cache, "v_cache", proj.dtype)
+        if k_cache.shape[2:] != (n_k_heads, key_dim) or v_cache.shape[2:] != (n_v_heads, value_dim) or \
+                k_cache.shape[:2] != v_cache.shape[:2]:
+            raise KernelError(f"attn_prepare: caches {tuple(k_cache.shape)} / {tuple(v_cache.shape)} do not fit")
+        num_pages, page_size = k_cache.shape[0], k_cache.shape[1]
+    f = _fn("attn_prepare", "jv_attn_prepare",
+            [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+             c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+             c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(proj.data_ptr(), _code(proj, "proj"), proj.stride(0), int(q_off), int(k_off), int(v_off), q_out.data_ptr(),
+             positions.data_ptr(), token_entry.data_ptr(), block_table.data_ptr(), block_table.shape[1], _ptr(inv_freq),
+             rot_dim, _ptr(q_norm_w), _ptr(k_norm_w), w_code, float(eps), float(temp_coef), int(temp_every),
+             _ptr(k_cache), _ptr(v_cache), n, n_q_heads, n_k_heads, n_v_heads, key_dim, value_dim, page_size, num_pages,
+             _status_ptr(proj.device), _stream()), "attn_prepare")
+
+
+def attn_finish(a: torch.Tensor, out: torch.Tensor, heads: int, value_dim: int, maps: int = 1, lam: float = 0.0,
+                unit_norm_eps: float | None = None, post: float = 1.0, gate: torch.Tensor | None = None) -> torch.Tensor:
+    """Heads after attention, before the output projection (csrc/attn_finish.cu): with `maps` == 2 the difference
+    a[:, h] - lam * a[:, heads + h] of two score maps on the same values; a weightless RMSNorm over each head
+    (`unit_norm_eps`) times `post`; a sigmoid gate, one number per head (`gate` [n, heads]) or per element
+    ([n, heads * value_dim]), which may be a column range of a wider tensor.  `a` [n, maps * heads * value_dim] is
+    float32 or of the type of `out`; `out` [n, heads * value_dim] may be a column range of a wider tensor."""
+    _cuda(a, "a"); _cuda(out, "out", contiguous=False)
+    n = a.shape[0]
+    if a.shape[1] != maps * heads * value_dim or out.shape != (n, heads * value_dim) or out.stride(1) != 1:
+        raise KernelError("attn_finish: shapes do not fit")
+    kind, g_stride = 0, 0
+    if gate is not None:
+        _cuda(gate, "gate", out.dtype, contiguous=False)
+        if gate.stride(1) != 1 or gate.shape[0] != n or gate.shape[1] not in (heads, heads * value_dim):
+            raise KernelError("attn_finish: the gate is [n, heads] or [n, heads * value size]")
+        kind = 2 if gate.shape[1] == heads * value_dim and value_dim > 1 else 1
+        g_stride = gate.stride(0)
+    f = _fn("attn_finish", "jv_attn_finish", [c_void_p, c_int, c_void_p, c_int, c_longlong, c_void_p, c_longlong, c_int,
+                                              c_int, c_int, c_int, c_int, c_float, c_int, c_float, c_float, c_void_p])
+    _check(f(a.data_ptr(), _code(a, "a"), out.data_ptr(), _code(out, "out"), out.stride(0), _ptr(gate), g_stride, kind,
+             n, heads, value_dim, maps, float(lam), 0 if unit_norm_eps is None else 1, float(unit_norm_eps or 0.0),
+             float(post), _stream()), "attn_finish")
+    return out
+
+
+UNARY_ACTIVATIONS = {"relu2": 0}       # relu(z)^2
+
+
+def unary_act(z: torch.Tensor, kind: str, out: torch.Tensor | None = None) -> torch.Tensor:
+    """act(z) element by element (csrc/activation.cu); `z` and `out` may be column ranges of wider tensors."""
+    _cuda(z, "z", contiguous=False)
+    n, cols = z.shape
+    if out is None:
+        out = torch.empty((n, cols), dtype=z.dtype, device=z.device)
+    _cuda(out, "out", z.dtype, contiguous=False)
+    if z.stride(1) != 1 or out.stride(1) != 1 or out.shape != z.shape:
+        raise KernelError("unary_act: unit column strides and equal shapes")
+    f = _fn("activation", "jv_unary_act", [c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(z.data_ptr(), z.stride(0), out.data_ptr(), out.stride(0), _code(z, "z"), n, cols, UNARY_ACTIVATIONS[kind],
+             _stream()), "unary_act")
+    return out
 
 
 MMA_HEAD_DIMS = (16, 32, 64, 128)      # head sizes the tensor-core attention kernels are instantiated for

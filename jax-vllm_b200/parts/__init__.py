@@ -1,5 +1,5 @@
-from . import (attention, block, feed_forward, latent_attention, norm, position, routed_experts,  # noqa: F401
-               token_input)  # noqa: F401  (register the built-in kinds)
+from . import (attention, block, dense_mlp, feed_forward, general_attention, latent_attention, norm,  # noqa: F401
+               position, routed_experts, token_input)  # noqa: F401  (register the built-in kinds)
 from .base import (BuildContext, FixedStateNeed, PagedKVNeed, PagedLayerCache, Part, StateLayerCache, StepContext,
                    TensorSpec)
 from .model import Model

@@ -39,6 +39,8 @@ class PagedKVNeed:
     head_dim: int
     window: Optional[int] = None
     shared_kv: bool = False       # the values are a leading part of the key rows: one tensor holds both
+    v_heads: Optional[int] = None     # value heads and value size where they differ from the keys' (key head g
+    v_head_dim: Optional[int] = None  # reads value head g % v_heads)
 
 
 @dataclass(frozen=True)

@@ -142,5 +142,77 @@ class BranchNormBlock(Part):
 register_block("branch_norm", BranchNormBlock)
 
 
+class ParallelBlock(Part):
+    """A layer whose two branches read ONE norm and are added together:
+
+        u = norm(h);   h <- h + (mixer(u) + feed_forward(u))          (the feed-forward is optional)
+
+    Where both parts offer their products (`in_weight`, `from_projection`, `out_weight`) and agree in type, the
+    block runs two products a layer instead of four: u times the stacked input matrices [W_mixer_in; W_up], and
+    the two parts' activations side by side times the output matrices joined along k, [W_o | W_down], whose sum
+    over k IS mixer(u) + feed_forward(u).  The sum is handed on un-added, like every block's last branch."""
+
+    def __init__(self, spec, prefix, ctx):
+        p = spec.prefix
+        self.spec, self.ctx = spec, ctx
+        self.mixer_norm = build(NORMS, "norm", spec.mixer_norm, p, ctx)
+        self.mixer = build(MIXERS, "mixer", spec.mixer, p, ctx)
+        self.feed_forward = None if spec.feed_forward is None else \
+            build(FEED_FORWARDS, "feed-forward", spec.feed_forward, p, ctx)
+        if spec.cache_from is not None:
+            if not hasattr(self.mixer, "writes_cache"):
+                raise ValueError(f"{p}: this mixer cannot read another layer's cache")
+            self.mixer.writes_cache = False
+        self.w_in = self.w_out = None
+
+    def parts(self):
+        return tuple(part for part in (self.mixer_norm, self.mixer, self.feed_forward) if part is not None)
+
+    def tensor_specs(self):
+        out = {}
+        for part in self.parts():
+            out.update(part.tensor_specs())
+        return out
+
+    def bind(self, tensors):
+        for part in self.parts():
+            part.bind(tensors)
+        both = [part for part in (self.mixer, self.feed_forward) if part is not None]
+        self.w_in = self.w_out = None
+        if all(hasattr(part, "from_projection") for part in both):
+            ins, outs = [part.in_weight() for part in both], [part.out_weight() for part in both]
+            if len({w.dtype for w in ins + outs}) == 1:
+                self.w_in = torch.cat(ins, dim=0).contiguous() if len(ins) > 1 else ins[0]
+                self.w_out = torch.cat(outs, dim=1).contiguous() if len(outs) > 1 else outs[0]
+
+    def forward(self, h, delta, step, cache):
+        step.stream_copy = None
+        dt = self.ctx.dtype
+        with trace_range("norm"):
+            u = self.mixer_norm.norm(h, delta)
+        if self.w_in is None:                       # parts without the packed interface: two branches, two sums
+            with trace_range("mixer"):
+                a = self.mixer.forward(u, step, cache)
+            if self.feed_forward is None:
+                return h, a
+            ops.residual_add(h, a)
+            with trace_range("feed_forward"):
+                return h, self.feed_forward.forward(u, step)
+        with trace_range("in"):
+            row = ops.linear(u, self.w_in, dt)
+        rm, km = self.mixer.in_rows, self.mixer.heads_out
+        acts = torch.empty((step.n_tokens, self.w_out.shape[1]), dtype=dt, device=row.device)
+        with trace_range("mixer"):
+            self.mixer.from_projection(row[:, :rm], step, cache, acts[:, :km])
+        if self.feed_forward is not None:
+            with trace_range("feed_forward"):
+                self.feed_forward.from_projection(row[:, rm:], step, acts[:, km:])
+        with trace_range("out"):
+            return h, ops.linear(acts, self.w_out, dt, parts_ok=True)
+
+
+register_block("parallel", ParallelBlock)
+
+
 def build_block(spec, ctx):
     return build(BLOCKS, "block", spec, spec.prefix, ctx)

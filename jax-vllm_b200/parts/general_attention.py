@@ -1,0 +1,182 @@
+"""Causal grouped-query attention over the paged cache whose options are data (`GeneralAttentionSpec`).
+
+    row  = x @ [W_q; W_k; W_v; W_g]^T                    one product over the packed matrix
+    q, k   whole-projection RMSNorm, query temperature, rotation of a leading part of every head;
+           k, v -> cache (v = k as projected where the spec says so)      csrc/attn_prepare.cu, 32-bit
+    a    = sum_j w_ij v_j over the visible keys, w = softmax(cap(q.k * scale)) or sigmoid(q.k * scale + bias_h)
+    o    = a, or a1 - lam * a2 for two score maps, unit-normed; times a sigmoid gate        csrc/attn_finish.cu
+    y    = o @ W_o^T
+
+Keys have `key_dim` elements a head and values `value_dim`; the value cache has its own shape.  With two score
+maps the rows of W_q and W_k are re-ordered when the weights are bound, from head by head [map 1 | map 2] to all
+heads' map 1 followed by all heads' map 2: the attention kernel then sees 2H query heads on 2G key heads with
+the ordinary grouping (query head i on key head i // (H/G)), and key head g reads value head g % G.
+
+The part also offers its two products to an arrangement that packs them with another part's
+(`in_weight`, `from_projection`, `out_weight`): both then read the same normed input in one product and add
+their outputs in one product over the concatenated inputs.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import ops
+from .base import PagedKVNeed, Part, TensorSpec
+from .registry import POSITIONS, build, register_mixer
+
+
+class GeneralAttention(Part):
+    kernels = ("attn_prepare", "attn_simt", "attn_finish", "gemm_simt")
+    FOREVER = 1 << 30
+
+    def __init__(self, spec, prefix, ctx):
+        self.spec, self.ctx = spec, ctx
+        self.prefix = f"{prefix}.{spec.prefix}" if spec.prefix else prefix
+        self.h, self.g, self.d, self.dv = spec.num_heads, spec.num_kv_heads, spec.key_dim, spec.value_dim
+        if self.h < 1 or self.g < 1 or self.h % self.g:
+            raise ValueError(f"{self.h} query heads are not a multiple of {self.g} key/value heads")
+        if spec.weights not in ("softmax", "sigmoid"):
+            raise ValueError(f"attention weights {spec.weights!r} are not built (softmax and sigmoid are)")
+        if spec.gate not in (None, "head", "element"):
+            raise ValueError(f"output gate {spec.gate!r} is not built (head and element are)")
+        if spec.values_from_keys and self.dv != self.d:
+            raise ValueError("values that are the keys have the keys' size")
+        if spec.twin is not None and spec.weights != "softmax":
+            raise ValueError("two score maps are built for softmax weights")
+        self.maps = 2 if spec.twin is not None else 1
+        self.hq, self.hk, self.hv = self.maps * self.h, self.maps * self.g, self.g     # as the kernels see them
+        self.position = build(POSITIONS, "position encoding", spec.position, self.prefix, ctx) \
+            if spec.position is not None else None
+        if self.position is not None and self.position.dim > self.d:
+            raise ValueError("rotary dim exceeds the key size")
+        self.writes_cache = True
+        self.w_in = self.w_o = self.q_norm = self.k_norm = self.bias = None
+        self.lam = 0.0
+        # columns of the packed projection
+        self.k_off = self.hq * self.d
+        self.v_off = -1 if spec.values_from_keys else self.k_off + self.hk * self.d
+        self.g_off = self.k_off + self.hk * self.d + (0 if spec.values_from_keys else self.hv * self.dv)
+        self.g_rows = {None: 0, "head": self.h, "element": self.h * self.dv}[spec.gate]
+        self.in_rows = self.g_off + self.g_rows
+        self.heads_out = self.h * self.dv
+
+    # -------------------------------------------------------------------- weights
+    def _names(self):
+        keys = ("q", "k", "v", "g", "o", "q_norm", "k_norm", "bias")
+        return {k: f"{self.prefix}.{n}" for k, n in zip(keys, self.spec.names)}
+
+    def tensor_specs(self):
+        n, s = self._names(), self.spec
+        specs = {n["q"]: TensorSpec((self.hq * self.d, s.hidden_size)),
+                 n["k"]: TensorSpec((self.hk * self.d, s.hidden_size)),
+                 n["o"]: TensorSpec((s.hidden_size, self.heads_out))}
+        if not s.values_from_keys:
+            specs[n["v"]] = TensorSpec((self.hv * self.dv, s.hidden_size))
+        if s.gate is not None:
+            specs[n["g"]] = TensorSpec((self.g_rows, s.hidden_size))
+        if s.whole_norm_eps is not None:
+            specs[n["q_norm"]] = TensorSpec((self.hq * self.d,), kind="vector", init="ones_normal")
+            specs[n["k_norm"]] = TensorSpec((self.hk * self.d,), kind="vector", init="ones_normal")
+        if s.score_bias:
+            specs[n["bias"]] = TensorSpec((self.h,), kind="vector", init="normal")
+        if s.twin is not None:
+            for name in s.twin.names:
+                specs[f"{self.prefix}.{name}"] = TensorSpec((self.d,), kind="vector", init="normal")
+        return specs
+
+    def _maps_first(self, w: torch.Tensor, heads: int) -> torch.Tensor:
+        """Rows [head][map][d] -> [map][head][d]."""
+        if self.maps == 1:
+            return w
+        return w.reshape(heads, self.maps, self.d, -1).transpose(0, 1).reshape(w.shape)
+
+    def bind(self, tensors):
+        n, s = self._names(), self.spec
+        mats = [self._maps_first(tensors[n["q"]], self.h), self._maps_first(tensors[n["k"]], self.g)]
+        if not s.values_from_keys:
+            mats.append(tensors[n["v"]])
+        if s.gate is not None:
+            mats.append(tensors[n["g"]])
+        mats = [self.compute_weight(m, self.ctx) for m in mats]
+        if len({m.dtype for m in mats}) > 1:
+            mats = [m.to(torch.float32) for m in mats]
+        self.w_in = torch.cat(mats, dim=0).contiguous()
+        self.w_o = self.compute_weight(tensors[n["o"]], self.ctx).contiguous()
+        if s.whole_norm_eps is not None:
+            self.q_norm, self.k_norm = tensors[n["q_norm"]].contiguous(), tensors[n["k_norm"]].contiguous()
+            if self.q_norm.dtype != self.k_norm.dtype:
+                self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
+        if s.score_bias:
+            self.bias = tensors[n["bias"]].to(torch.float32).contiguous()
+        if s.twin is not None:
+            lq1, lk1, lq2, lk2 = (tensors[f"{self.prefix}.{name}"].double() for name in s.twin.names)
+            self.lam = math.exp(float((lq1 * lk1).sum())) - math.exp(float((lq2 * lk2).sum())) + float(s.twin.offset)
+
+    # ---------------------------------------------------------------------- cache
+    def cache_need(self):
+        if self.hv == self.hk and self.dv == self.d:
+            return PagedKVNeed(self.hk, self.d, None)
+        return PagedKVNeed(self.hk, self.d, None, v_heads=self.hv, v_head_dim=self.dv)
+
+    def tile_classes(self, page_size: int):
+        return [(ops.attn_simt_tokens_per_tile(self.hq, self.hk), 2, self.FOREVER)]
+
+    # ----------------------------------------------------------------------- step
+    def in_weight(self) -> torch.Tensor:
+        return self.w_in
+
+    def out_weight(self) -> torch.Tensor:
+        return self.w_o
+
+    def forward(self, x, step, cache):
+        dt = self.ctx.dtype
+        row = ops.linear(x, self.w_in, dt)
+        heads = torch.empty((step.n_tokens, self.heads_out), dtype=dt, device=x.device)
+        self.from_projection(row, step, cache, heads)
+        return ops.linear(heads, self.w_o, dt, parts_ok=True)
+
+    def from_projection(self, row, step, cache, out):
+        """`row` [n, in_rows] (the packed projection, possibly a column range of a wider tensor) -> the heads
+        before the output projection, written to `out` [n, heads * value_dim] (possibly a column range)."""
+        s, dt, n = self.spec, self.ctx.dtype, step.n_tokens
+        table = step.block_tables[cache.group]
+        writes = self.writes_cache and cache.writes
+        q = torch.empty((n, self.hq * self.d), dtype=dt, device=row.device)
+        coef, every = s.query_temperature if s.query_temperature is not None else (0.0, 0)
+        ops.attn_prepare(row, 0, self.k_off, self.v_off, q, step.positions, step.token_entry, table,
+                         self.position.table() if self.position is not None else None, self.q_norm, self.k_norm,
+                         s.whole_norm_eps or 0.0, coef, every, cache.k if writes else None, cache.v if writes else None,
+                         self.hq, self.hk, self.hv, self.d, self.dv)
+        gate = row[:, self.g_off:self.g_off + self.g_rows] if s.gate is not None else None
+        twin = s.twin
+        direct = twin is None and gate is None and out.is_contiguous()
+        # two maps are subtracted in 32-bit: the attention kernel leaves them as floats
+        a = out if direct else torch.empty((n, self.hq * self.dv), dtype=torch.float32 if twin is not None else dt,
+                                           device=row.device)
+        self.attend(q, a, step, cache, table)
+        if not direct:
+            ops.attn_finish(a, out, self.h, self.dv, maps=self.maps, lam=self.lam,
+                            unit_norm_eps=None if twin is None else twin.eps,
+                            post=1.0 if twin is None else 1.0 - twin.offset, gate=gate)
+        return out
+
+    def attend(self, q, a, step, cache, table):
+        s = self.spec
+        common = (cache.k, cache.v, table, step.cu_seqlens, step.start_pos)
+        extra = dict(v_dim=self.dv, score_cap=s.score_cap or 0.0, sigmoid=s.weights == "sigmoid", bias=self.bias)
+        for cls in self.tile_classes(cache.k.shape[1]):
+            work, n_work = step.tile_work[cls]
+            if n_work:
+                ops.attn_simt(q, q.stride(0), a, *common, work, n_work, self.hq, self.hk, self.d, 0, s.scale, **extra)
+        dwork, n_dec = step.decode_work
+        if n_dec:
+            split = self.ctx.decode_split_size
+            n_splits = max(1, -(-step.max_seq_len // split))
+            ops.attn_simt(q, q.stride(0), a, *common, dwork, n_dec, self.hq, self.hk, self.d, 0, s.scale,
+                          split_size=split, n_splits=n_splits, **extra)
+
+
+register_mixer("general_attention", GeneralAttention)

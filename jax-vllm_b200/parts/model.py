@@ -24,6 +24,7 @@ class Model(Part):
         # (or state) for each.  A layer with `cache_from` reads the cache of the latest
         # earlier place at which the layer it names ran.
         self.order = tuple(spec.run_order())
+        self.reinject = frozenset(spec.reinject)
         self.place_cache = []
         self.place_names = [f"layer {i}" if self.order.count(i) == 1 else f"layer {i} (place {k})"
                             for k, i in enumerate(self.order)]
@@ -92,15 +93,26 @@ class Model(Part):
         return sorted(classes)
 
     # ----------------------------------------------------------------------- step
-    def forward(self, step, caches) -> torch.Tensor:
-        """Logits [n_logit_rows, vocab] float32 for one batch; caches are updated in place."""
+    def forward(self, step, caches, tap=None) -> torch.Tensor:
+        """Logits [n_logit_rows, vocab] float32 for one batch; caches are updated in place.  `tap(place, stream)`,
+        if given, is called after every place of the run order with a copy of the stream as that layer leaves
+        it (for comparing a model layer by layer; it costs a pass over the stream per layer)."""
         with ops.trace_range("embedding"):
             h = ops.embed_gather(self.embedding, step.token_ids)
         delta = None
         step.stream_copy = None
         for k, i in enumerate(self.order):
+            if k in self.reinject:
+                # the embedding output enters the stream again, after what the layer before left un-added
+                if delta is not None:
+                    ops.residual_add(h, delta)
+                    delta = None
+                step.stream_copy = None
+                ops.embed_gather(self.embedding, step.token_ids, out=h, accumulate=True)
             with ops.trace_range(self.place_names[k]):
                 h, delta = self.layers[i].forward(h, delta, step, caches[self.place_cache[k]])
+            if tap is not None:
+                tap(k, h.clone() if delta is None else ops.residual_add(h.clone(), delta))
         if step.n_logit_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
         with ops.trace_range("final_norm"):

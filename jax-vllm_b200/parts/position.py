@@ -16,7 +16,8 @@ class Rope(Part):
         if spec.dim % 2 or spec.dim < 2:
             raise ValueError(f"rotary dim must be even and positive, got {spec.dim}")
         self.dim, self.theta = int(spec.dim), float(spec.theta)
-        exponents = torch.arange(0, self.dim, 2, dtype=torch.float32) / self.dim
+        wide = torch.float64 if getattr(spec, "exact_table", False) else torch.float32
+        exponents = torch.arange(0, self.dim, 2, dtype=wide) / self.dim
         self.inv_freq = (1.0 / (self.theta ** exponents)).to(torch.float32).to(ctx.device)
 
     def table(self):

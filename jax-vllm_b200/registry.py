@@ -54,6 +54,9 @@ def _register_builtin() -> None:
     from .models.guronex import ARCHITECTURE as GURONEX, GuronexConfig
 
     register_architecture(GURONEX, GuronexConfig)
+    from .models.loselix import ARCHITECTURE as LOSELIX, LoselixConfig
+
+    register_architecture(LOSELIX, LoselixConfig)
 
 
 _register_builtin()
