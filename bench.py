@@ -517,6 +517,40 @@ def design_configs(z, layers, vocab=32000):
     return guronex, qwen
 
 
+# Layer sizes for `--design loselix`: three layers, one of each of its mixers (softmax attention with a gate a head;
+# sigmoid attention over normed projections; two capped score maps on shared values), each with a relu-squared
+# feed-forward of `ff`, beside the Qwen3 dense layer of equal width, heads and feed-forward work per token
+# (3 * intermediate = 2 * ff).  "w2k" and "w4k": heads of 128 throughout (two maps of 64 on values of 128), the sizes
+# of 1B- and 8B-class models; "mix": heads of 64, 96 and 48/96, which run on the mma.sync kernels.
+LOSELIX_SIZES = {
+    "w2k": dict(width=2048, heads=16, kv=4, ff=8448, soft=(128, 128, 64), sig=128, twin=(64, 128, 32)),
+    "w4k": dict(width=4096, heads=32, kv=8, ff=18432, soft=(128, 128, 64), sig=128, twin=(64, 128, 32)),
+    "mix": dict(width=2048, heads=16, kv=4, ff=8448, soft=(64, 64, 32), sig=96, twin=(48, 96, 12)),
+}
+LOSELIX_KINDS = ("soft", "sigmoid", "twin")
+
+
+def loselix_configs(z, layers, vocab=32000):
+    H, G = z["heads"], z["kv"]
+    sd, sv, sr = z["soft"]
+    td, tv, tr = z["twin"]
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    three = [{"type": "attention_2", "mlp": dict(mlp),
+              "mixer": {"heads": H, "kv_heads": G, "dim": sd, "vdim": sv, "scale": sd ** -0.5, "rot": {"base": 5e5, "dims": sr}}},
+             {"type": "attention_3", "mlp": dict(mlp),
+              "mixer": {"heads": H, "kv_heads": G, "dim": z["sig"], "vdim": z["sig"], "scale": z["sig"] ** -0.5,
+                        "q_temp": {"coef": 0.3, "every": 128}}},
+             {"type": "attention", "mlp": dict(mlp),
+              "mixer": {"heads": H, "kv_heads": G, "dim": td, "vdim": tv, "scale": td ** -0.5, "softcap": 50.0, "diff": 0.3,
+                        "rot": {"base": 2.5e5, "dims": tr}}}]
+    loselix = {"architecture": "Loselix", "vocab": vocab, "width": z["width"], "norm": {"eps": 1e-6},
+               "layers": [dict(three[i % 3]) for i in range(layers)]}
+    inter = -(-(2 * z["ff"] // 3) // 128) * 128
+    qwen = dict(QWEN3_8B, vocab_size=vocab, hidden_size=z["width"], intermediate_size=inter, num_hidden_layers=layers,
+                num_attention_heads=H, num_key_value_heads=G, head_dim=128)
+    return loselix, qwen
+
+
 def time_part(fn, reps, flush):
     """Median device time (us) of `fn`, captured into a CUDA graph (so that the host's launches do not count) and
     replayed one at a time, the L2 written over in between."""
@@ -538,7 +572,7 @@ def time_part(fn, reps, flush):
     return statistics.median(times)
 
 
-def design_parts(model, kind, z, inter, batch, tokens, reps, pk):
+def design_parts(model, kind, z, inter, batch, tokens, reps, pk, layer_index=0):
     """The attention kernel alone, the whole mixer and the whole feed-forward of layer 0: one prompt of `tokens`
     tokens, then one decode step of `batch` requests at CONTEXT tokens; each with its roofline (the slower of its
     FLOPs at the measured bf16 peak and its bytes, weights and cache rows read once, at the measured copy bandwidth)."""
@@ -548,7 +582,7 @@ def design_parts(model, kind, z, inter, batch, tokens, reps, pk):
     W, H = z["width"], z["heads"]
     flush = torch.zeros(160 << 20, dtype=torch.int16, device="cuda")
     out = {}
-    layer = model.layers[0]
+    layer = model.layers[layer_index]
     for phase in ("prefill", "decode"):
         if phase == "prefill":
             driver = make_driver(model, max_num_seqs=1, max_model_len=tokens + 16, block_size=PAGE, prefix_cache=False,
@@ -566,7 +600,7 @@ def design_parts(model, kind, z, inter, batch, tokens, reps, pk):
             entries = [StepEntry(rc, [b], (0,)) for b, rc in enumerate(rcs)]
             n, pairs = batch, batch * (CONTEXT + 1)
         step = driver.runner.builder.build(entries)
-        cache = driver.runner.layer_caches[0]
+        cache = driver.runner.layer_caches[layer_index]
         table = step.block_tables[cache.group]
         x = (torch.randn((n, W), device="cuda") * 0.5).to(torch.bfloat16)
         mixer, ff = layer.mixer, layer.feed_forward
@@ -578,6 +612,15 @@ def design_parts(model, kind, z, inter, batch, tokens, reps, pk):
             attn_flops, attn_bytes = 2 * H * (dk + dc) * pairs, keys * dk * 2 + n * H * (dk + dc) * 2
             hit = z["experts"] * (1 - (1 - z["top"] / z["experts"]) ** n)           # experts that some token chose, about
             ff_flops, ff_bytes = 2 * n * z["top"] * 2 * z["ff"] * W, hit * 2 * z["ff"] * W * 2
+        elif kind == "loselix":
+            hq, hk, hv, dk, dv = mixer.hq, mixer.hk, mixer.hv, mixer.d, mixer.dv     # as the kernels see them
+            q = torch.randn((n, hq * dk), device="cuda").to(torch.bfloat16)
+            a = torch.empty((n, hq * dv), dtype=torch.float32 if mixer.maps == 2 else torch.bfloat16, device="cuda")
+            attn = lambda: mixer.attend(q, a, step, cache, table)
+            keys = tokens if phase == "prefill" else batch * (CONTEXT + 1)
+            attn_flops = 2 * hq * (dk + dv) * pairs
+            attn_bytes = keys * (hk * dk + hv * dv) * 2 + n * hq * (dk * 2 + dv * a.element_size())
+            ff_flops, ff_bytes = 2 * n * 2 * z["ff"] * W, 2 * z["ff"] * W * 2
         else:
             hkv = mixer.hkv
             qkv = torch.randn((n, (H + 2 * hkv) * 128), device="cuda").to(torch.bfloat16)
@@ -606,11 +649,14 @@ def design_parts(model, kind, z, inter, batch, tokens, reps, pk):
 
 
 def design(name: str, layers, sizes, steps, warmup) -> int:
-    """`--design guronex`: prefill and decode throughput of the Guronex design at a few layer sizes beside the Qwen3
-    dense model of equal size (random weights, `--layers` layers, default 4), and the attention kernel, the mixer
-    and the feed-forward of one layer each alone with their rooflines."""
+    """`--design guronex|loselix`: prefill and decode throughput of that design at a few layer sizes beside the Qwen3
+    dense model of equal size (random weights, `--layers` layers, default 4; 3 for loselix, one of each mixer), and
+    the attention kernel, the mixer and the feed-forward of one layer (for loselix: of each kind of layer) each alone
+    with their rooflines."""
     import torch
     from jax_vllm_b200 import random_model, registry
+    if name == "loselix":
+        return design_loselix(layers or 3, sizes, steps, warmup)
     if name != "guronex":
         print(f"bench.py: no design {name!r}")
         return 2
@@ -633,6 +679,39 @@ def design(name: str, layers, sizes, steps, warmup) -> int:
                              decode_tok_s=round(8 / (dms / 1e3), 1), decode_ms_per_step=round(dms, 4),
                              decode_launches_per_step=launches, clocks=clocks.summary)
             row[kind]["parts"] = design_parts(model, kind, z, q_cfg["intermediate_size"], 8, PREFILL_TOKENS, 7, pk)
+            del model
+            torch.cuda.empty_cache()
+        out["sizes"][tag] = row
+    print(json.dumps(out))
+    return 0
+
+
+def design_loselix(layers, sizes, steps, warmup) -> int:
+    import torch
+    from jax_vllm_b200 import random_model, registry
+    pk, pk_src = peaks()
+    sizes = [t for t in sizes if t in LOSELIX_SIZES] or list(LOSELIX_SIZES)
+    out = {"design": "loselix", "layers": layers, "prefill_tokens": PREFILL_TOKENS, "decode_batch": 8, "context": CONTEXT,
+           "dtype": "bf16", "data": "synthetic (random weights, seed 5)", "peaks": pk, "peak_source": pk_src, "sizes": {}}
+    for tag in sizes:
+        z = LOSELIX_SIZES[tag]
+        l_cfg, q_cfg = loselix_configs(z, layers)
+        row = {"loselix": {"config": dict(z)}, "qwen3": {"config": {
+            "hidden": z["width"], "heads": z["heads"], "kv_heads": z["kv"], "head_dim": 128,
+            "intermediate": q_cfg["intermediate_size"]}}}
+        for kind, cfg in (("loselix", l_cfg), ("qwen3", q_cfg)):
+            model = random_model(registry.config_from_dict(cfg), seed=5, dtype="bf16", device="cuda:0")
+            with ClockSampler() as clocks:
+                pms = time_prefill(model, PREFILL_TOKENS, warmup=2, reps=5)
+                dms, launches, _, _ = time_decode(model, 8, steps, warmup)
+            row[kind].update(prefill_tok_s=round(PREFILL_TOKENS / (pms / 1e3), 1), prefill_ms=round(pms, 3),
+                             decode_tok_s=round(8 / (dms / 1e3), 1), decode_ms_per_step=round(dms, 4),
+                             decode_launches_per_step=launches, clocks=clocks.summary)
+            if kind == "qwen3":
+                row[kind]["parts"] = design_parts(model, kind, z, q_cfg["intermediate_size"], 8, PREFILL_TOKENS, 7, pk)
+            else:
+                row[kind]["parts"] = {LOSELIX_KINDS[i]: design_parts(model, kind, z, 0, 8, PREFILL_TOKENS, 7, pk, layer_index=i)
+                                      for i in range(min(3, layers))}
             del model
             torch.cuda.empty_cache()
         out["sizes"][tag] = row
@@ -666,9 +745,11 @@ def main():
     ap.add_argument("--with-workloads", action="store_true",
                     help="after the headline run, also run the two serving workloads and add their lines under `workloads`")
     ap.add_argument("--design", default=None, metavar="NAME",
-                    help="guronex: that design's prefill and decode throughput at a few layer sizes beside Qwen3 of "
-                         "equal size, with the rooflines of its attention and feed-forward (see design())")
-    ap.add_argument("--sizes", default="lite,mid,row576", help="with --design: which of its layer sizes, comma-separated")
+                    help="guronex or loselix: that design's prefill and decode throughput at a few layer sizes beside "
+                         "Qwen3 of equal size, with the rooflines of its attention and feed-forward (see design())")
+    ap.add_argument("--sizes", default="lite,mid,row576",
+                    help="with --design: which of its layer sizes, comma-separated (guronex: lite,mid,row576; loselix: "
+                         "w2k,w4k,mix, all by default)")
     ap.add_argument("--micro-eager", action="store_true",
                     help="with --micro: plain launches instead of replays of a CUDA graph (for a profiler)")
     args = ap.parse_args()

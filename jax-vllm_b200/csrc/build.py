@@ -81,13 +81,33 @@ def _find_build_dir() -> Path:
     raise BuildError(f"no writable build folder among {[str(c) for c in cands]}")
 
 
+# Sources that are compiled once per pair of sizes: the library `<source>@<a>x<b>` is the source with these two
+# macros set to a and b (the plain name gives the source's own defaults).
+SIZED = {"attn_general_mma": ("JV_KEY_DIM", "JV_VALUE_DIM")}
+
+
+def _source(name: str) -> str:
+    return name.partition("@")[0]
+
+
 def _extra_flags(name: str) -> list[str]:
-    return []
+    base, _, variant = name.partition("@")
+    if not variant:
+        return []
+    if base not in SIZED:
+        raise BuildError(f"{base}.cu is not compiled per size")
+    try:
+        sizes = [int(v) for v in variant.split("x")]
+    except ValueError:
+        sizes = []
+    if len(sizes) != len(SIZED[base]) or min(sizes) < 1:
+        raise BuildError(f"{name}: expected {base}@" + "x".join("<n>" for _ in SIZED[base]))
+    return [f"-D{macro}={v}" for macro, v in zip(SIZED[base], sizes)]
 
 
 def _hash(name: str) -> str:
     h = hashlib.sha256()
-    for f in [f"{name}.cu", *HEADERS, *DEPENDS.get(name, [])]:
+    for f in [f"{_source(name)}.cu", *HEADERS, *DEPENDS.get(_source(name), [])]:
         h.update((SRC_DIR / f).read_bytes())
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + _extra_flags(name)).encode())
     return h.hexdigest()[:16]
@@ -98,7 +118,7 @@ def library_path(name: str) -> Path:
 
 
 def _compile(name: str, out: Path) -> None:
-    src = SRC_DIR / f"{name}.cu"
+    src = SRC_DIR / f"{_source(name)}.cu"
     if not src.is_file():
         raise BuildError(f"no kernel source {src}")
     tmp = out.with_suffix(f".tmp{os.getpid()}.so")
@@ -106,7 +126,7 @@ def _compile(name: str, out: Path) -> None:
     env = dict(os.environ)
     env.setdefault("TMPDIR", str(out.parent))  # nvcc's intermediates: somewhere writable
     t0 = time.time()
-    print(f"[jax-vllm_b200] compiling {src.name} for sm_100a ...", file=sys.stderr, flush=True)
+    print(f"[jax-vllm_b200] compiling {src.name} for sm_100a ... {' '.join(_extra_flags(name))}", file=sys.stderr, flush=True)
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env, text=True)
     while True:
         try:

@@ -433,6 +433,65 @@ def attn_simt(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.
              _status_ptr(q.device), _stream()), "attn_simt", launches=2 if n_splits > 0 else 1)
 
 
+GENERAL_MMA_MAX_KEY, GENERAL_MMA_MAX_VALUE = 256, 128
+
+
+def attn_general_mma_supports(dtype: torch.dtype, key_dim: int, value_dim: int) -> bool:
+    """Whether the tensor-core kernel for keys and values of different sizes takes these (csrc/attn_general_mma.cu):
+    bfloat16, sizes in steps of 16."""
+    return (dtype == torch.bfloat16 and key_dim % 16 == 0 and value_dim % 16 == 0
+            and 16 <= key_dim <= GENERAL_MMA_MAX_KEY and 16 <= value_dim <= GENERAL_MMA_MAX_VALUE)
+
+
+def attn_general_mma_library(key_dim: int, value_dim: int) -> str:
+    """The library of the kernel for this pair of sizes (compiled when first asked for)."""
+    return f"attn_general_mma@{int(key_dim)}x{int(value_dim)}"
+
+
+def attn_general_mma_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
+    return 64 // min(n_q_heads // n_kv_heads, 16)
+
+
+def attn_general_mma(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                     block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor,
+                     n_work: int, n_q_heads: int, n_kv_heads: int, scale: float, split_size: int = 0, n_splits: int = 0,
+                     score_cap: float = 0.0, sigmoid: bool = False, bias: torch.Tensor | None = None) -> None:
+    """Paged causal attention on the tensor cores with the options of `attn_simt`: the key size is the key
+    cache's row, the value size and the value heads the value cache's; bfloat16 in, bfloat16 or float32 out."""
+    for t, nm in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache")):
+        _cuda(t, nm, torch.bfloat16, contiguous=(nm != "q"))
+    _cuda(out, "out", contiguous=False)
+    for t, nm in ((block_table, "block_table"), (cu_seqlens, "cu_seqlens"), (start_pos, "start_pos"), (work, "work")):
+        _cuda(t, nm, torch.int32)
+    if n_work == 0:
+        return
+    if out.dtype not in (torch.bfloat16, torch.float32) or out.stride(1) != 1:
+        raise KernelError("attn_general_mma: out must be bfloat16 or float32 with unit column stride")
+    if k_cache.dim() != 4 or v_cache.dim() != 4 or k_cache.shape[:2] != v_cache.shape[:2] or \
+            k_cache.shape[2] != n_kv_heads or n_kv_heads % v_cache.shape[2]:
+        raise KernelError(f"attn_general_mma: caches {tuple(k_cache.shape)} / {tuple(v_cache.shape)} do not fit")
+    key_dim, n_v_heads, value_dim = k_cache.shape[3], v_cache.shape[2], v_cache.shape[3]
+    if bias is not None:
+        _cuda(bias, "bias", torch.float32)
+        if bias.numel() != n_q_heads:
+            raise KernelError("attn_general_mma: one bias per query head")
+    part_o = part_ml = counters = None
+    if n_splits > 0:
+        part_o = torch.empty(n_work * n_q_heads * n_splits * value_dim, dtype=torch.float32, device=q.device)
+        part_ml = torch.empty(n_work * n_q_heads * n_splits * 2, dtype=torch.float32, device=q.device)
+        counters = _split_counters(q.device, n_work * n_kv_heads * (-(-(n_q_heads // n_kv_heads) // 16)))
+    f = _fn(attn_general_mma_library(key_dim, value_dim), "jv_attn_general_mma",
+            [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+             c_int, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(f(q.data_ptr(), q_stride, out.data_ptr(), out.stride(0), 1 if out.dtype == torch.float32 else 0, _ptr(part_o),
+             _ptr(part_ml), _ptr(counters), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
+             block_table.shape[1], cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(), n_work, n_q_heads,
+             n_kv_heads, n_v_heads, key_dim, value_dim, k_cache.shape[1], k_cache.shape[0], 0, float(scale),
+             float(score_cap), 1 if sigmoid else 0, _ptr(bias), int(split_size), int(n_splits), _status_ptr(q.device),
+             _stream()), "attn_general_mma")
+
+
 def attn_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor, positions: torch.Tensor,
                  token_entry: torch.Tensor, block_table: torch.Tensor, inv_freq: torch.Tensor | None,
                  q_norm_w, k_norm_w, eps: float, temp_coef: float, temp_every: int, k_cache, v_cache,

@@ -24,6 +24,8 @@ import math
 import torch
 
 from .. import ops
+from ..config.model_spec import AttentionSpec
+from .attention import Attention
 from .base import PagedKVNeed, Part, TensorSpec
 from .registry import POSITIONS, build, register_mixer
 
@@ -53,6 +55,21 @@ class GeneralAttention(Part):
         if self.position is not None and self.position.dim > self.d:
             raise ValueError("rotary dim exceeds the key size")
         self.writes_cache = True
+        # Which attention kernel: once queries and keys are prepared, a mixer with one softmax map, no cap and
+        # values shaped like its keys IS the plain grouped-query attention, and goes the way of that mixer (the
+        # tcgen05 kernels for heads of 128, mma.sync for 16/32/64, in bfloat16).  Every other bfloat16 mixer with
+        # sizes in steps of 16 takes the tensor-core kernel compiled for its pair of sizes; the rest, and 32-bit,
+        # the CUDA-core kernel.
+        plain = (spec.twin is None and spec.weights == "softmax" and not spec.score_cap and self.hv == self.hk
+                 and self.dv == self.d)
+        self.plain = self.general = None
+        if plain and ops.attn_mma_supports(ctx.dtype, self.d):
+            self.plain = Attention(AttentionSpec(spec.hidden_size, self.hq, self.hk, self.d, spec.scale, prefix=""),
+                                   self.prefix, ctx)
+            self.kernels += tuple(k for k in self.plain.kernels if k not in self.kernels and k != "rope_kv")
+        elif ops.attn_general_mma_supports(ctx.dtype, self.d, self.dv):
+            self.general = ops.attn_general_mma_library(self.d, self.dv)
+            self.kernels += (self.general,)
         self.w_in = self.w_o = self.q_norm = self.k_norm = self.bias = None
         self.lam = 0.0
         # columns of the packed projection
@@ -122,6 +139,10 @@ class GeneralAttention(Part):
         return PagedKVNeed(self.hk, self.d, None, v_heads=self.hv, v_head_dim=self.dv)
 
     def tile_classes(self, page_size: int):
+        if self.plain is not None:
+            return self.plain.tile_classes(page_size)
+        if self.general is not None:
+            return [(ops.attn_general_mma_tokens_per_tile(self.hq, self.hk), 2, self.FOREVER)]
         return [(ops.attn_simt_tokens_per_tile(self.hq, self.hk), 2, self.FOREVER)]
 
     # ----------------------------------------------------------------------- step
@@ -165,18 +186,25 @@ class GeneralAttention(Part):
 
     def attend(self, q, a, step, cache, table):
         s = self.spec
+        if self.plain is not None:
+            return self.plain.attend(q, a, step, cache, table)
         common = (cache.k, cache.v, table, step.cu_seqlens, step.start_pos)
-        extra = dict(v_dim=self.dv, score_cap=s.score_cap or 0.0, sigmoid=s.weights == "sigmoid", bias=self.bias)
+        extra = dict(score_cap=s.score_cap or 0.0, sigmoid=s.weights == "sigmoid", bias=self.bias)
+        if self.general is not None:
+            def kernel(work, n_work, **split):
+                ops.attn_general_mma(q, q.stride(0), a, *common, work, n_work, self.hq, self.hk, s.scale, **split, **extra)
+        else:
+            def kernel(work, n_work, **split):
+                ops.attn_simt(q, q.stride(0), a, *common, work, n_work, self.hq, self.hk, self.d, 0, s.scale,
+                              v_dim=self.dv, **split, **extra)
         for cls in self.tile_classes(cache.k.shape[1]):
             work, n_work = step.tile_work[cls]
             if n_work:
-                ops.attn_simt(q, q.stride(0), a, *common, work, n_work, self.hq, self.hk, self.d, 0, s.scale, **extra)
+                kernel(work, n_work)
         dwork, n_dec = step.decode_work
         if n_dec:
             split = self.ctx.decode_split_size
-            n_splits = max(1, -(-step.max_seq_len // split))
-            ops.attn_simt(q, q.stride(0), a, *common, dwork, n_dec, self.hq, self.hk, self.d, 0, s.scale,
-                          split_size=split, n_splits=n_splits, **extra)
+            kernel(dwork, n_dec, split_size=split, n_splits=max(1, -(-step.max_seq_len // split)))
 
 
 register_mixer("general_attention", GeneralAttention)
