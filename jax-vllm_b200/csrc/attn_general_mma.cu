@@ -4,7 +4,7 @@
 // one library per pair of sizes that a model needs, built when it is first asked for), and with these options:
 //
 //   value heads    the value cache is [pages, page, n_v_heads, VD]; key head g reads value head g % n_v_heads
-//   score cap      s <- cap * tanh(s / cap) on the scaled score (accurate tanh: the cap may be large)
+//   score cap      s <- cap * tanh(s / cap) on the scaled score
 //   sigmoid        the weight of a visible key is sigmoid(s + bias[query head]); no maximum, no sum, no division
 //   float output   two score maps are subtracted by the caller in 32-bit
 //
@@ -199,7 +199,9 @@ __device__ __forceinline__ void weights_tile(float (&s)[NB][4], float (&o)[VD / 
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       float v = s[nb][i] * scale;
-      if (cap > 0.f) v = cap * tanhf(v / cap);
+      // tanh(x) = 1 - 2 / (1 + e^(2x)): one ex2 and one division; its absolute error (about 1e-7) times the cap is
+      // far below what the 16-bit operands of the product leave in a score
+      if (cap > 0.f) v = cap * (1.f - 2.f / (1.f + fast_exp2(v * (2.f * LOG2E / cap))));
       s[nb][i] = v;
     }
   if (sigmoid) {

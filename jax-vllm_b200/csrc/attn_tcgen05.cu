@@ -51,6 +51,8 @@ struct Params {
   const int* cu_seqlens; const int* start_pos; const int* work;
   int n_work, n_q_heads, n_kv_heads, page_size, num_pages, hpt, tokens_per_tile;
   float scale_log2;
+  int sigmoid;                 // 1: the weight of a visible key is sigmoid(score * scale + bias[query head]): no maximum,
+  const float* bias;           //    no sum, no division ([n_q_heads] floats or null)
   int* status;
 };
 
@@ -135,6 +137,12 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
         "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
       : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+// 1 / x to about 2^-23 relative (1 / inf = 0): the weights it makes are rounded to bfloat16 right away
+__device__ __forceinline__ float fast_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -446,6 +454,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
       const int n_tiles = it.n_tiles, j_hi = it.j_hi, pos_first = it.pos_first;
       const bool row_ok = t < it.tokens_here && hh < G;
       const int pos = row_ok ? pos_first + t : -1;
+      // sigmoid weights: the bias of this row's head, in the exponent's unit
+      const float bias_log2 = (p.sigmoid && p.bias != nullptr && row_ok) ? p.bias[it.kv_head * G + hh] * LOG2E : 0.f;
       // m_ref is the reference maximum that the exponentials are taken against.  It follows the true
       // maximum lazily: only when the maximum has grown by more than 2^8 (in the exponent) is O rescaled,
       // which is rare after the first tiles; until then probabilities may exceed 1 by at most that factor.
@@ -486,7 +496,8 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
         // ---- the reference moves only if some score of the tile has outgrown it (always in a row's first tile
         // with keys, rarely later): one barrier tells all 256 threads whether any row is in that case, and only
         // then do the two threads of a row exchange their maxima
-        const bool outgrown = ok && my_max != -INFINITY && (m_ref == -INFINITY || (my_max - m_ref) * p.scale_log2 > LAZY);
+        const bool outgrown = !p.sigmoid && ok && my_max != -INFINITY &&
+                              (m_ref == -INFINITY || (my_max - m_ref) * p.scale_log2 > LAZY);
         float alpha = 1.f;
         if (pair_barrier_or(quad, outgrown)) {
           sh->xch[half][row] = my_max;
@@ -519,8 +530,22 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
         if (!ok) continue;
         // ---- probabilities: pairs of scores in packed 32-bit arithmetic, as bfloat16 pairs into this thread's 32
         // columns of the P buffer (column c of a row holds its keys 2c and 2c+1)
-        float sum[4];
-        {
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+        if (p.sigmoid) {
+          // every weight stands alone: 1 / (1 + 2^-(s * scale + bias)); a hidden key (-inf) gives 1 / inf = 0
+          const float neg_scale = -p.scale_log2, neg_bias = -bias_log2;
+          uint32_t pw[32];
+#pragma unroll
+          for (int c = 0; c < 2; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float e0 = fast_exp2(fmaf(__uint_as_float(sr[c][i]), neg_scale, neg_bias));
+              const float e1 = fast_exp2(fmaf(__uint_as_float(sr[c][i + 1]), neg_scale, neg_bias));
+              const __nv_bfloat162 h = __floats2bfloat162_rn(fast_rcp(1.f + e0), fast_rcp(1.f + e1));
+              pw[c * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+          tmem_st32_bits(tmem + lane_addr + TMEM_P + (gt & 1) * 64 + half * 32, pw);
+        } else {
           const uint64_t scale2 = pack2(p.scale_log2, p.scale_log2), neg_m2 = pack2(-m_scaled, -m_scaled);
           uint64_t sum2[2] = {pack2(0.f, 0.f), pack2(0.f, 0.f)};
           uint32_t pw[32];
@@ -572,7 +597,7 @@ __global__ void __launch_bounds__(THREADS, 1) attn_tcgen05_kernel(const __grid_c
       const float l_row = sh->xch[0][row] + sh->xch[1][row];
       pair_barrier(quad);                                        // both have read before the next item's first tile writes
       const bool got = ok && mbar_wait(&sh->o_done[g_last & 1], (g_last >> 1) & 1);
-      const float inv = row_ok ? 1.f / l_row : 0.f;
+      const float inv = row_ok ? (p.sigmoid ? 1.f : 1.f / l_row) : 0.f;
       const bool whole = it.tokens_here == p.tokens_per_tile;
       // A whole tile leaves through shared memory (where the item's queries were: every product with them has
       // completed) and one TMA store per half of the head; threads that write their 128 bytes to rows 8 KB apart in
@@ -676,10 +701,12 @@ JV_EXPORT int jv_attn_tcgen05_tokens_per_tile(int n_q_heads, int n_kv_heads) { r
 // q: [n_tokens, q_stride] bfloat16 with head h of a token at column h*128; out: [n_tokens, out_stride];
 // k_cache/v_cache: [num_pages, page_size, n_kv_heads, 128]; work: [n_work, 2] (entry, first token of the tile),
 // tiles of jv_attn_tcgen05_tokens_per_tile tokens, in ascending order of work.
-JV_EXPORT int jv_attn_tcgen05(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
-                              const void* v_cache, const int* block_table, int table_width, const int* cu_seqlens,
-                              const int* start_pos, const int* work, int n_work, int n_q_heads, int n_kv_heads,
-                              int head_dim, int page_size, int num_pages, float scale, int* status, cudaStream_t stream) {
+// sigmoid != 0: the weights are sigmoid(q.k * scale + bias[query head]) instead of a softmax (bias: [n_q_heads] floats or null).
+JV_EXPORT int jv_attn_tcgen05_ex(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
+                                 const void* v_cache, const int* block_table, int table_width, const int* cu_seqlens,
+                                 const int* start_pos, const int* work, int n_work, int n_q_heads, int n_kv_heads,
+                                 int head_dim, int page_size, int num_pages, float scale, int sigmoid, const float* bias,
+                                 int* status, cudaStream_t stream) {
   if (n_work == 0) return JV_OK;
   if (!jv_attn_tcgen05_supports(head_dim, n_q_heads, n_kv_heads, page_size, 0)) return JV_ERR_UNSUPPORTED;
   if ((q_stride % 8) || (out_stride % 8) || ((uintptr_t)q % 16) || ((uintptr_t)out % 16) || ((uintptr_t)k_cache % 16) ||
@@ -715,7 +742,7 @@ JV_EXPORT int jv_attn_tcgen05(const void* q, int q_stride, int n_tokens, void* o
   p.out = (__nv_bfloat16*)out; p.out_stride = out_stride; p.block_table = block_table; p.table_width = table_width;
   p.cu_seqlens = cu_seqlens; p.start_pos = start_pos; p.work = work; p.n_work = n_work; p.n_q_heads = n_q_heads; p.n_kv_heads = n_kv_heads;
   p.page_size = page_size; p.num_pages = num_pages; p.hpt = G; p.tokens_per_tile = ROWS / G;
-  p.scale_log2 = scale * LOG2E; p.status = status;
+  p.scale_log2 = scale * LOG2E; p.status = status; p.sigmoid = sigmoid ? 1 : 0; p.bias = bias;
   constexpr size_t smem = TILE_BYTES * (Q_BUFFERS + K_STAGES + V_STAGES) + sizeof(Shared) + 1024;
   static bool ready[JV_MAX_DEVICES];
   if (!jv_once_per_device(ready, [&] {
@@ -732,4 +759,13 @@ JV_EXPORT int jv_attn_tcgen05(const void* q, int q_stride, int n_tokens, void* o
   const long long items = (long long)n_work * n_kv_heads;
   const int blocks = items < sm_count[dev] ? (int)items : sm_count[dev];
   return jv_launch(attn_tcgen05_kernel, dim3(blocks), dim3(THREADS), smem, stream, q_map, k_map, v_map, out_map, p);
+}
+
+JV_EXPORT int jv_attn_tcgen05(const void* q, int q_stride, int n_tokens, void* out, int out_stride, const void* k_cache,
+                              const void* v_cache, const int* block_table, int table_width, const int* cu_seqlens,
+                              const int* start_pos, const int* work, int n_work, int n_q_heads, int n_kv_heads,
+                              int head_dim, int page_size, int num_pages, float scale, int* status, cudaStream_t stream) {
+  return jv_attn_tcgen05_ex(q, q_stride, n_tokens, out, out_stride, k_cache, v_cache, block_table, table_width, cu_seqlens,
+                            start_pos, work, n_work, n_q_heads, n_kv_heads, head_dim, page_size, num_pages, scale, 0, nullptr,
+                            status, stream);
 }

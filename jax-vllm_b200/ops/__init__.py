@@ -702,9 +702,11 @@ def attn_tcgen05_tokens_per_tile(n_q_heads: int, n_kv_heads: int) -> int:
 
 def attn_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                  block_table: torch.Tensor, cu_seqlens: torch.Tensor, start_pos: torch.Tensor, work: torch.Tensor,
-                 n_work: int, n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float) -> None:
+                 n_work: int, n_q_heads: int, n_kv_heads: int, head_dim: int, scale: float, sigmoid: bool = False,
+                 bias: torch.Tensor | None = None) -> None:
     """Paged causal attention of prompt portions on tcgen05 tensor cores with scores and output in tensor
-    memory (csrc/attn_tcgen05.cu); `work` lists 128-row tiles of `attn_tcgen05_tokens_per_tile` tokens."""
+    memory (csrc/attn_tcgen05.cu); `work` lists 128-row tiles of `attn_tcgen05_tokens_per_tile` tokens.  With
+    `sigmoid` the weight of a visible key is sigmoid(score * scale + bias[query head]) instead of a softmax."""
     for t, nm in ((q, "q"), (out, "out"), (k_cache, "k_cache"), (v_cache, "v_cache")):
         _cuda(t, nm, torch.bfloat16, contiguous=(nm not in ("q", "out")))     # q and out may be some heads of wider rows
     if out.stride(1) != 1 or q.stride(1) != 1:
@@ -713,13 +715,17 @@ def attn_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, k_cache: tor
         _cuda(t, nm, torch.int32)
     if n_work == 0:
         return
-    f = _fn("attn_tcgen05", "jv_attn_tcgen05", [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                                                c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                c_float, c_void_p, c_void_p])
+    if bias is not None:
+        _cuda(bias, "bias", torch.float32)
+        if bias.numel() != n_q_heads:
+            raise KernelError("attn_tcgen05: one bias per query head")
+    f = _fn("attn_tcgen05", "jv_attn_tcgen05_ex", [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                                   c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                                   c_float, c_int, c_void_p, c_void_p, c_void_p])
     _check(f(q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), out.stride(0), k_cache.data_ptr(), v_cache.data_ptr(),
              block_table.data_ptr(), block_table.shape[1], cu_seqlens.data_ptr(), start_pos.data_ptr(), work.data_ptr(),
              n_work, n_q_heads, n_kv_heads, head_dim, k_cache.shape[1], k_cache.shape[0], float(scale),
-             _status_ptr(q.device), _stream()), "attn_tcgen05")
+             1 if sigmoid else 0, _ptr(bias), _status_ptr(q.device), _stream()), "attn_tcgen05")
 
 
 DECODE_TCGEN05_MAX_REQUESTS = 512

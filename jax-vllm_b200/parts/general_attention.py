@@ -70,6 +70,11 @@ class GeneralAttention(Part):
         elif ops.attn_general_mma_supports(ctx.dtype, self.d, self.dv):
             self.general = ops.attn_general_mma_library(self.d, self.dv)
             self.kernels += (self.general,)
+        # sigmoid weights on heads of 128: prompt portions that fill a 128-row tile go to the tcgen05 kernel
+        self.sigmoid_tiles = (self.general is not None and spec.weights == "sigmoid" and not spec.score_cap
+                              and self.hv == self.hk and self.dv == self.d == 128)
+        if self.sigmoid_tiles:
+            self.kernels += ("attn_tcgen05",)
         self.w_in = self.w_o = self.q_norm = self.k_norm = self.bias = None
         self.lam = 0.0
         # columns of the packed projection
@@ -142,7 +147,12 @@ class GeneralAttention(Part):
         if self.plain is not None:
             return self.plain.tile_classes(page_size)
         if self.general is not None:
-            return [(ops.attn_general_mma_tokens_per_tile(self.hq, self.hk), 2, self.FOREVER)]
+            small = ops.attn_general_mma_tokens_per_tile(self.hq, self.hk)
+            if self.sigmoid_tiles and ops.attn_tcgen05_supports(self.ctx.dtype, self.d, self.hq, self.hk, page_size, 0):
+                big = ops.attn_tcgen05_tokens_per_tile(self.hq, self.hk)
+                if big > small:
+                    return [(small, 2, big), (big, big, self.FOREVER)]
+            return [(small, 2, self.FOREVER)]
         return [(ops.attn_simt_tokens_per_tile(self.hq, self.hk), 2, self.FOREVER)]
 
     # ----------------------------------------------------------------------- step
@@ -199,7 +209,10 @@ class GeneralAttention(Part):
                               v_dim=self.dv, **split, **extra)
         for cls in self.tile_classes(cache.k.shape[1]):
             work, n_work = step.tile_work[cls]
-            if n_work:
+            if n_work and cls[1] > 2:                      # the class of whole 128-row tiles
+                ops.attn_tcgen05(q, q.stride(0), a, *common, work, n_work, self.hq, self.hk, self.d, s.scale,
+                                 sigmoid=True, bias=self.bias)
+            elif n_work:
                 kernel(work, n_work)
         dwork, n_dec = step.decode_work
         if n_dec:

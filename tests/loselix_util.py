@@ -54,10 +54,11 @@ LA = config(200, 64, [layer(soft(4, 1, 32, 32, rot=16), 48),
 LB = config(131, 72, [layer(twin(3, 3, 24, 40, rot=6, base=2e4, softcap=30.0, diff=0.4), 56),
                       layer(sig(6, 2, 20, coef=0.5, every=16), None),
                       layer(soft(2, 1, 24, 8, rot=24, base=500.0), 100)], eps=3e-6)
-# heads of 128 (the tcgen05 kernels for the softmax mixer), eight query heads on two key heads, a loop over the
-# first two layers that runs three times before the third layer, no query temperature, no rotation in the twin layer
+# heads of 128 (the tcgen05 kernels for the softmax mixer, and for whole tiles of the sigmoid mixer), eight query heads
+# on two key heads, a loop over the first two layers that runs three times before the third layer, no query
+# temperature, no rotation in the twin layer
 LC = config(320, 128, [layer(soft(8, 2, 128, 128, rot=64, base=5e5), 192),
-                       layer(sig(4, 4, 64, every=0), 128),
+                       layer(sig(4, 2, 128, every=0), 128),
                        layer(twin(4, 2, 64, 64, softcap=0.0, diff=0.1), 64)], eps=1e-5, loop=(0, 2, 3))
 # one layer, one head, values of a size of its own: sizes of one
 LD = config(90, 40, [layer(soft(1, 1, 16, 24, rot=2), 8)], eps=1e-5, loop=(0, 1, 1))

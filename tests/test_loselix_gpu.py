@@ -255,6 +255,46 @@ def test_attention_kernels_alone(name, kernel):
         at += q
 
 
+@pytest.mark.parametrize("Hq,Hk", [(4, 2), (3, 3), (8, 1)])
+def test_sigmoid_weights_on_the_tcgen05_kernel(Hq, Hk):
+    """Whole 128-row tiles of a prompt portion with sigmoid weights and a bias per head, heads of 128, earlier context
+    in the cache, a last tile that is not full, and an entry that is exactly one tile."""
+    from jax_vllm_b200 import ops
+    D, P, n_pages, scale = 128, 16, 40, 128 ** -0.5
+    tpt = ops.attn_tcgen05_tokens_per_tile(Hq, Hk)
+    ctx_new = [(100, 2 * tpt + 22), (0, tpt)]
+    g = torch.Generator().manual_seed(Hq)
+    table = scrambled_pages(ctx_new, P, n_pages, g)
+    kc = torch.full((n_pages, P, Hk, D), float("nan"), dtype=torch.bfloat16)
+    vc = torch.full((n_pages, P, Hk, D), float("nan"), dtype=torch.bfloat16)
+    ks, vs, qs = [], [], []
+    for e, (c, q) in enumerate(ctx_new):
+        k = (torch.randn((c + q, Hk, D), generator=g) * 1.5).to(torch.bfloat16)
+        v = torch.randn((c + q, Hk, D), generator=g).to(torch.bfloat16)
+        for j in range(c + q):
+            kc[table[e, j // P], j % P], vc[table[e, j // P], j % P] = k[j], v[j]
+        ks.append(k.double()); vs.append(v.double())
+        qs.append((torch.randn((q, Hq, D), generator=g) * 1.5).to(torch.bfloat16))
+    bias = torch.randn(Hq, generator=g) - 2.0
+    n = sum(q for _, q in ctx_new)
+    q_all = torch.cat(qs).reshape(n, Hq * D).cuda()
+    cu = torch.tensor([0, ctx_new[0][1], n], dtype=torch.int32).cuda()
+    start = torch.tensor([c for c, _ in ctx_new], dtype=torch.int32).cuda()
+    out = torch.full((n, Hq * D), float("nan"), dtype=torch.bfloat16).cuda()
+    tiles = [(e, t) for e, (_, q) in enumerate(ctx_new) for t in range(0, q, tpt)]
+    ops.attn_tcgen05(q_all, Hq * D, out, kc.cuda(), vc.cuda(), table.cuda(), cu, start,
+                     torch.tensor(tiles, dtype=torch.int32).cuda(), len(tiles), Hq, Hk, D, scale, sigmoid=True, bias=bias.cuda())
+    ops.check_status()
+    got = out.cpu().double().view(n, Hq, D)
+    at = 0
+    for e, (c, q) in enumerate(ctx_new):
+        q_full = torch.zeros((c + q, Hq, D), dtype=torch.float64)
+        q_full[c:] = qs[e].double()
+        want = lp.sigmoid_attend(lp.causal_scores(q_full, ks[e], scale), bias.double(), vs[e])[c:]
+        assert (got[at:at + q] - want).abs().max() < 2.5e-2 * max(1.0, want.abs().max().item())
+        at += q
+
+
 def test_a_size_pair_outside_the_tensor_core_kernel_is_told():
     from jax_vllm_b200 import ops
     assert not ops.attn_general_mma_supports(torch.bfloat16, 24, 32)
@@ -518,3 +558,37 @@ def test_random_arrivals_with_few_pages(tmp_path):
     w = stored(weights)
     for i, prompt in enumerate(prompts):
         assert d.requests[ids[i]].output_ids == plain_greedy(c, w, prompt, new_tokens[i]), f"request {i}"
+
+
+def test_command_line(tmp_path):
+    """cli.py as a user runs it on a Loselix folder: prompts as token ids, 32-bit; the printed ids are the plain
+    implementation's greedy tokens (prefix reuse is on by default: the second prompt repeats the first one's start)."""
+    c = CONFIGS["le"]
+    weights = make_weights(c, seed=23)
+    folder = write_folder(tmp_path / "model", c, weights)
+    prompts = [random_tokens(37, c["vocab"], seed=60), random_tokens(37, c["vocab"], seed=60)[:33] + [5, 6], [9]]
+    cmd = [sys.executable, str(ROOT / "cli.py"), "--model-path", str(folder), "--dtype", "fp32", "--max-tokens", "7",
+           "--max-model-len", "128", "--block-size", "32", "--no-prewarm"]
+    for p in prompts:
+        cmd += ["--prompt-ids", ",".join(map(str, p))]
+    proc = subprocess.run(cmd, capture_output=True, text=True, env=dict(os.environ), timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    got = [json.loads(line)["output_ids"] for line in proc.stdout.splitlines() if line.startswith("{")]
+    assert got == [plain_greedy(c, stored(weights), p, 7) for p in prompts]
+
+
+def test_sampled_tokens_depend_on_the_seed_not_on_the_batch(tmp_path):
+    """Temperature sampling through the entry point: a request's tokens depend on its seed, not on what runs beside it."""
+    from jax_vllm_b200 import SamplingParams, generate, load_from_path, make_driver
+    c = CONFIGS["ld"]
+    folder = write_folder(tmp_path / "model", c, make_weights(c, seed=24))
+    model = load_from_path(folder, dtype="fp32")
+    prompts = [random_tokens(n, c["vocab"], seed=70 + n) for n in (11, 3, 25)]
+    sp = [SamplingParams(max_new_tokens=12, temperature=0.8, seed=100 + i) for i in range(3)]
+    together = generate(make_driver(model, max_num_seqs=3, max_model_len=64, block_size=4), prompts, sp)
+    alone = [generate(make_driver(model, max_num_seqs=1, max_model_len=64, block_size=4), [p], [s])[0]
+             for p, s in zip(prompts, sp)]
+    assert together == alone
+    other = generate(make_driver(model, max_num_seqs=1, max_model_len=64, block_size=4), [prompts[0]],
+                     [SamplingParams(max_new_tokens=12, temperature=0.8, seed=999)])[0]
+    assert other != alone[0]
