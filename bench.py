@@ -262,7 +262,9 @@ def micro(spec: str, reps: int, eager: bool = False) -> int:
     attn_decode_tcgen05:<B>:<CTX>[:<SPLIT>[:<PAGE>]]   the same with the tcgen05 kernel
     (the decode kernels are timed as replays of a CUDA graph of one launch per cache, as the engine runs them)
     attn_prefill:<T>     prompt attention of one request of T tokens (8B head layout), mma.sync kernel
-    attn_prefill_tcgen05:<T>[:<PAGE>]   the same with the tcgen05 kernel"""
+    attn_prefill_tcgen05:<T>[:<PAGE>]   the same with the tcgen05 kernel
+    attn_general:<T>:<HQ>:<HK>:<HV>:<KD>:<VD>[:<CAP>[:sigmoid]]   prompt attention of one request of T tokens with the mma.sync
+                         kernel compiled for keys of KD and values of VD (HQ query, HK key, HV value heads)"""
     import torch
     from jax_vllm_b200 import ops
     kind, *rest = spec.split(":")
@@ -288,6 +290,37 @@ def micro(spec: str, reps: int, eager: bool = False) -> int:
         torch.cuda.synchronize()
         us = start.elapsed_time(end) / reps * 1e3
         print(json.dumps({"micro": spec, "us": round(us, 2), "TFLOP/s": round(2.0 * m * n * k / us / 1e6, 1)}))
+        return 0
+    if kind == "attn_general":
+        T, hq, hk, hv, kd, vd = (int(v) for v in rest[:6])
+        cap = float(rest[6]) if len(rest) > 6 else 0.0
+        sigmoid = "sigmoid" in rest[7:]
+        page = PAGE
+        num_pages = -(-T // page)
+        table = torch.randperm(num_pages).to(torch.int32).view(1, -1).to(dev)
+        kc = torch.randn(num_pages, page, hk, kd, device=dev).to(torch.bfloat16)
+        vc = torch.randn(num_pages, page, hv, vd, device=dev).to(torch.bfloat16)
+        q = torch.randn(T, hq * kd, device=dev).to(torch.bfloat16)
+        out = torch.empty(T, hq * vd, device=dev, dtype=torch.bfloat16)
+        cu = torch.tensor([0, T], dtype=torch.int32, device=dev)
+        st = torch.zeros(1, dtype=torch.int32, device=dev)
+        tpt = ops.attn_general_mma_tokens_per_tile(hq, hk)
+        work = torch.tensor([[0, t] for t in range(0, T, tpt)], dtype=torch.int32, device=dev)
+        bias = torch.zeros(hq, device=dev) if sigmoid else None
+        run = lambda i: ops.attn_general_mma(q, hq * kd, out, kc, vc, table, cu, st, work, work.shape[0], hq, hk, kd ** -0.5,
+                                             score_cap=cap, sigmoid=sigmoid, bias=bias)
+        for i in range(3):
+            run(i)
+        torch.cuda.synchronize()
+        start.record()
+        for i in range(reps):
+            run(i)
+        end.record()
+        torch.cuda.synchronize()
+        ops.check_status()
+        us = start.elapsed_time(end) / reps * 1e3
+        flops = 2.0 * hq * (kd + vd) * T * (T + 1) / 2
+        print(json.dumps({"micro": spec, "us": round(us, 2), "TFLOP/s": round(flops / us / 1e6, 1)}))
         return 0
     if kind == "linear":
         n, k = (int(v) for v in rest[0].split("x"))
