@@ -145,11 +145,46 @@ __global__ void unary_act_kernel(const T* __restrict__ in, long long in_stride, 
   }
 }
 
+// The same, 16 bytes per access (columns and row strides multiples of the vector length, 16-byte aligned bases).
+template <typename T>
+__global__ void unary_act_vec_kernel(const T* __restrict__ in, long long in_stride, T* __restrict__ out, long long out_stride,
+                                     int cols, size_t total_vec, int kind) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int V = 16 / sizeof(T);
+  const int vec_per_row = cols / V;
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < total_vec; idx += stride) {
+    const size_t n = idx / vec_per_row;
+    const int i = (int)(idx - n * vec_per_row) * V;
+    const uint4 z4 = *reinterpret_cast<const uint4*>(in + n * in_stride + i);
+    const T* z = reinterpret_cast<const T*>(&z4);
+    uint4 o4;
+    T* o = reinterpret_cast<T*>(&o4);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float r = fmaxf(to_f32(z[k]), 0.f);
+      o[k] = from_f32<T>(r * r);
+    }
+    *reinterpret_cast<uint4*>(out + n * out_stride + i) = o4;
+  }
+}
+
 JV_EXPORT int jv_unary_act(const void* in, long long in_stride, void* out, long long out_stride, int dtype, int n, int cols,
                            int kind, cudaStream_t stream) {
   const size_t total = (size_t)n * cols;
   if (total == 0) return JV_OK;
   if (kind != 0) return JV_ERR_UNSUPPORTED;
+  const int vec = dtype == 0 ? 4 : 8;
+  if (cols % vec == 0 && in_stride % vec == 0 && out_stride % vec == 0 && ((uintptr_t)in % 16) == 0 && ((uintptr_t)out % 16) == 0) {
+    const size_t total_vec = total / vec;
+    size_t blocks = (total_vec + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    JV_DISPATCH_DTYPE(dtype, T, return jv_launch(unary_act_vec_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,
+                                                  (const T*)in, in_stride, (T*)out, out_stride, cols, total_vec, kind));
+    return JV_ERR_UNSUPPORTED;
+  }
   size_t blocks = (total + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
   JV_DISPATCH_DTYPE(dtype, T, return jv_launch(unary_act_kernel<T>, dim3((int)blocks), dim3(256), 0, stream,

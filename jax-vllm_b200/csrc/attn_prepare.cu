@@ -1,5 +1,5 @@
 // Query/key/value preparation for attention mixers whose heads are not all alike, fused with the
-// write of the new keys and values into the paged cache.  One block handles one token of a packed
+// write of the new keys and values into the paged cache.  A few blocks handle one token of a packed
 // projection row `proj` (queries at q_off, keys at k_off, values at v_off; element offsets):
 //
 //   whole-projection RMSNorm (optional, queries and keys separately): all heads of a token form ONE
@@ -18,6 +18,7 @@
 
 namespace {
 constexpr int THREADS = 128;
+constexpr int ELEMS_PER_BLOCK = 4 * THREADS;
 
 struct PrepareParams {
   const void* proj; long long row_stride; int q_off, k_off, v_off;
@@ -31,44 +32,45 @@ struct PrepareParams {
   int* status;
 };
 
-// One vector of `heads` heads of `dim` elements: norm over the whole vector (if w), a common factor, rotation.
+// One element of a vector of heads of `dim` elements: the common factor (norm, temperature), the norm's weight,
+// and for the first rot_dim elements of a head the rotation with its partner (cosines and sines of the token's
+// position come from shared memory: trig[j] = cos, trig[half + j] = sin).
 template <typename T, typename TW>
-__device__ void prepare_vector(const T* __restrict__ src, T* __restrict__ dst, long long dst_head_stride, int heads,
-                               int dim, const TW* __restrict__ w, float eps, float factor,
-                               const float* __restrict__ inv_freq, int rot_dim, int pos, float* scratch) {
-  const int total = heads * dim;
-  float inv = 1.f;
-  if (w != nullptr) {
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < total; i += THREADS) {
-      const float v = to_f32(src[i]);
-      ss += v * v;
-    }
-    ss = block_sum(ss, scratch);
-    inv = qk_norm_factor(ss, total, eps);
+__device__ __forceinline__ float prepare_element(const T* __restrict__ src, int i, int dim, const TW* __restrict__ w,
+                                                 float factor, const float* trig, int rot_dim) {
+  const int head = i / dim, d = i - head * dim;
+  float v = to_f32(src[i]) * factor;
+  if (w != nullptr) v *= to_f32(w[i]);
+  if (d < rot_dim) {
+    const int half = rot_dim >> 1;
+    const int j = d < half ? d : d - half;
+    const int ip = d < half ? i + half : i - half;          // the partner of the pair
+    float u = to_f32(src[ip]) * factor;
+    if (w != nullptr) u *= to_f32(w[ip]);
+    float first, second;
+    if (d < half) qk_rotate_pair(v, u, trig[j], trig[half + j], &first, &second);
+    else qk_rotate_pair(u, v, trig[j], trig[half + j], &first, &second);
+    v = d < half ? first : second;
   }
-  const int half = rot_dim >> 1;
-  for (int i = threadIdx.x; i < total; i += THREADS) {
-    const int head = i / dim, d = i - head * dim;
-    float v = to_f32(src[i]) * inv * factor;
-    if (w != nullptr) v *= to_f32(w[i]);
-    if (d < rot_dim) {
-      const int j = d < half ? d : d - half;
-      const int ip = d < half ? i + half : i - half;          // the partner of the pair
-      float u = to_f32(src[ip]) * inv * factor;
-      if (w != nullptr) u *= to_f32(w[ip]);
-      float sn, cs, first, second;
-      qk_rotation(pos, inv_freq[j], &sn, &cs);
-      if (d < half) qk_rotate_pair(v, u, cs, sn, &first, &second);
-      else qk_rotate_pair(u, v, cs, sn, &first, &second);
-      v = d < half ? first : second;
-    }
-    dst[(long long)head * dst_head_stride + d] = from_f32<T>(v);
-  }
+  return v;
 }
 
+template <typename T>
+__device__ __forceinline__ float sum_of_squares(const T* __restrict__ src, int n, float* scratch) {
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += THREADS) {
+    const float v = to_f32(src[i]);
+    ss += v * v;
+  }
+  return block_sum(ss, scratch);
+}
+
+// grid = (tokens, parts): a block handles ELEMS_PER_BLOCK consecutive elements of the token's [queries | keys |
+// values]; every block of a token forms the token's cosines and sines and (for whole-projection norms) the sums of
+// squares itself, which is a few thousand elements read from the L2.
 template <typename T, typename TW>
 __global__ void __launch_bounds__(THREADS) attn_prepare_kernel(const PrepareParams p) {
+  extern __shared__ float trig[];                            // [rot_dim / 2] cosines, [rot_dim / 2] sines
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
@@ -76,27 +78,49 @@ __global__ void __launch_bounds__(THREADS) attn_prepare_kernel(const PreparePara
   const int pos = p.positions[n];
   const T* row = (const T*)p.proj + (size_t)n * p.row_stride;
   const int D = p.key_dim, DV = p.value_dim;
+  const bool writes = p.k_cache != nullptr;
+  const int nq = p.n_q_heads * D, nk = writes ? p.n_k_heads * D : 0, nv = writes ? p.n_v_heads * DV : 0;
+  const int first = blockIdx.y * ELEMS_PER_BLOCK, last = min(first + ELEMS_PER_BLOCK, nq + nk + nv);
+  const int half = p.rot_dim >> 1;
+  for (int j = threadIdx.x; j < half; j += THREADS) qk_rotation(pos, p.inv_freq[j], &trig[half + j], &trig[j]);
 
-  float temp = 1.f;
-  if (p.temp_every > 0) temp = 1.f + p.temp_coef * logf((float)((pos + 1) / p.temp_every) + 1.f);
-  prepare_vector<T, TW>(row + p.q_off, (T*)p.q_out + (size_t)n * p.n_q_heads * D, D, p.n_q_heads, D,
-                        (const TW*)p.q_norm_w, p.eps, temp, p.inv_freq, p.rot_dim, pos, scratch);
-  if (p.k_cache == nullptr) return;
+  float q_factor = 1.f, k_factor = 1.f;
+  if (p.q_norm_w != nullptr && first < nq) q_factor = qk_norm_factor(sum_of_squares(row + p.q_off, nq, scratch), nq, p.eps);
+  if (p.k_norm_w != nullptr && last > nq && first < nq + nk)
+    k_factor = qk_norm_factor(sum_of_squares(row + p.k_off, nk, scratch), nk, p.eps);
+  if (p.temp_every > 0) q_factor *= 1.f + p.temp_coef * logf((float)((pos + 1) / p.temp_every) + 1.f);
+  __syncthreads();                                           // the cosines and sines are there
 
-  const int entry = p.token_entry[n];
-  const int page_idx = pos / p.page_size;
-  const int page = (page_idx < p.table_width) ? p.block_table[(size_t)entry * p.table_width + page_idx] : -1;
-  if (page < 0 || page >= p.num_pages) {
-    if (threadIdx.x == 0) atomicOr(p.status, JV_STATUS_BAD_PAGE);
-    return;
+  size_t slot = 0;
+  bool have_page = false;
+  if (writes && last > nq) {
+    const int entry = p.token_entry[n];
+    const int page_idx = pos / p.page_size;
+    const int page = (page_idx < p.table_width) ? p.block_table[(size_t)entry * p.table_width + page_idx] : -1;
+    if (page < 0 || page >= p.num_pages) {
+      if (threadIdx.x == 0) atomicOr(p.status, JV_STATUS_BAD_PAGE);
+    } else {
+      have_page = true;
+      slot = (size_t)page * p.page_size + (pos - page_idx * p.page_size);
+    }
   }
-  const size_t slot = (size_t)page * p.page_size + (pos - page_idx * p.page_size);
-  // values first: where they are the keys as projected they are read before anything else touches them
-  T* vdst = (T*)p.v_cache + slot * p.n_v_heads * DV;
-  const T* vsrc = row + (p.v_off >= 0 ? p.v_off : p.k_off);
-  for (int i = threadIdx.x; i < p.n_v_heads * DV; i += THREADS) vdst[i] = vsrc[i];
-  prepare_vector<T, TW>(row + p.k_off, (T*)p.k_cache + slot * p.n_k_heads * D, D, p.n_k_heads, D,
-                        (const TW*)p.k_norm_w, p.eps, 1.f, p.inv_freq, p.rot_dim, pos, scratch);
+  T* q_dst = (T*)p.q_out + (size_t)n * nq;
+  T* k_dst = (T*)p.k_cache + slot * nk;
+  T* v_dst = (T*)p.v_cache + slot * nv;
+  const T* v_src = row + (p.v_off >= 0 ? p.v_off : p.k_off);    // the values, or the keys as projected
+  for (int idx = first + threadIdx.x; idx < last; idx += THREADS) {
+    if (idx < nq) {
+      q_dst[idx] = from_f32<T>(prepare_element<T, TW>(row + p.q_off, idx, D, (const TW*)p.q_norm_w, q_factor, trig, p.rot_dim));
+    } else if (!have_page) {
+      continue;
+    } else if (idx < nq + nk) {
+      const int i = idx - nq;
+      k_dst[i] = from_f32<T>(prepare_element<T, TW>(row + p.k_off, i, D, (const TW*)p.k_norm_w, k_factor, trig, p.rot_dim));
+    } else {
+      const int i = idx - nq - nk;
+      v_dst[i] = v_src[i];
+    }
+  }
 }
 }  // namespace
 
@@ -123,9 +147,12 @@ JV_EXPORT int jv_attn_prepare(const void* proj, int dtype, long long row_stride,
   p.temp_coef = temp_coef; p.temp_every = temp_every; p.k_cache = k_cache; p.v_cache = v_cache;
   p.n_q_heads = n_q_heads; p.n_k_heads = n_k_heads; p.n_v_heads = n_v_heads; p.key_dim = key_dim;
   p.value_dim = value_dim; p.page_size = page_size; p.num_pages = num_pages; p.status = status;
+  const int total = n_q_heads * key_dim + (k_cache != nullptr ? n_k_heads * key_dim + n_v_heads * value_dim : 0);
+  const dim3 grid(n, (total + ELEMS_PER_BLOCK - 1) / ELEMS_PER_BLOCK);
+  const size_t smem = sizeof(float) * (rot_dim > 0 ? rot_dim : 1);
   JV_DISPATCH_DTYPE(dtype, T, {
-    if (w_dtype == 0) return jv_launch(attn_prepare_kernel<T, float>, dim3(n), dim3(THREADS), 0, stream, p);
-    if (w_dtype == 1) return jv_launch(attn_prepare_kernel<T, __nv_bfloat16>, dim3(n), dim3(THREADS), 0, stream, p);
+    if (w_dtype == 0) return jv_launch(attn_prepare_kernel<T, float>, grid, dim3(THREADS), smem, stream, p);
+    if (w_dtype == 1) return jv_launch(attn_prepare_kernel<T, __nv_bfloat16>, grid, dim3(THREADS), smem, stream, p);
   });
   return JV_ERR_UNSUPPORTED;
 }
