@@ -1,5 +1,5 @@
 """A single-GPU inference engine for NVIDIA B200 (sm_100a) in the shape of
-alec-tschantz/jax-vllm: model folder in, generated tokens out, for Qwen3 dense and Guronex.
+alec-tschantz/jax-vllm: model folder in, generated tokens out, for Qwen3 dense, Guronex and Loselix.
 
     from jax_vllm_b200 import load_from_path, make_driver, add_request, step, has_work
 """
