@@ -592,3 +592,59 @@ def test_sampled_tokens_depend_on_the_seed_not_on_the_batch(tmp_path):
     other = generate(make_driver(model, max_num_seqs=1, max_model_len=64, block_size=4), [prompts[0]],
                      [SamplingParams(max_new_tokens=12, temperature=0.8, seed=999)])[0]
     assert other != alone[0]
+
+
+def random_configuration(seed):
+    """A configuration drawn at random: every size, the order of the layers, the loop and which options are there."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([40, 64, 72, 96, 128, 136])
+    sizes = [8, 16, 24, 32, 48, 64, 80, 96, 128]
+    layers = []
+    for _ in range(rng.randint(1, 5)):
+        kv = rng.choice([1, 2, 3])
+        heads = kv * rng.choice([1, 2, 4])
+        dim, vdim = rng.choice(sizes), rng.choice(sizes)
+        kind = rng.choice(["soft", "sigmoid", "twin"])
+        rot = rng.choice([None, 2 * rng.randint(1, dim // 2)])
+        if kind == "soft":
+            mixer = soft(heads, kv, dim, rng.choice([dim, vdim]), rot=rot, base=rng.choice([1e4, 5e5]))
+        elif kind == "sigmoid":
+            mixer = sig(heads, kv, dim, coef=rng.uniform(0.1, 0.6), every=rng.choice([0, 3, 16, 50]))
+        else:
+            mixer = twin(heads, kv, dim, vdim, rot=rot, softcap=rng.choice([0.0, 8.0, 50.0]), diff=rng.uniform(0.1, 0.5))
+        layers.append(layer(mixer, rng.choice([None, 24, 56, 100])))
+    n = len(layers)
+    loop = None
+    if rng.random() < 0.7:
+        a = rng.randrange(n)
+        loop = (a, rng.randint(a + 1, n), rng.randint(1, 3))
+    return config(rng.choice([97, 160, 333]), width, layers, eps=rng.choice([1e-6, 1e-5]), loop=loop)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(seed, tmp_path):
+    """Sizes, layer orders, loops and options that nobody chose: portions of changing size, then single tokens, two
+    requests side by side, in both precisions."""
+    from jax_vllm_b200.engine.replay import Replayer
+    c = random_configuration(seed)
+    weights = make_weights(c, seed=100 + seed)
+    folder = write_folder(tmp_path / "model", c, weights)
+    seqs = {"a": random_tokens(75, c["vocab"], seed=seed), "b": random_tokens(41, c["vocab"], seed=50 + seed)}
+    want = {rid: lp.forward(c, stored(weights), t).to(torch.float32) for rid, t in seqs.items()}
+    plan = [{"a": 20}, {"a": 2, "b": 30}, {"a": 33, "b": 1}] + [{"a": 1, "b": 1}] * 10 + [{"a": 999}]
+    fed = {r: 0 for r in seqs}
+    steps = []
+    for k, row in enumerate(plan):
+        entries = []
+        for rid, n in row.items():
+            part = seqs[rid][fed[rid]:fed[rid] + n]
+            if part:
+                entries.append({"id": rid, "tokens": part, "want": list(range(len(part)))})
+                fed[rid] += len(part)
+        steps.append({"step": k, "entries": entries, "end": [e["id"] for e in entries if fed[e["id"]] == len(seqs[e["id"]])]})
+    for dtype in ("float32", "bfloat16"):
+        rep = Replayer(folder, dtype, tmp_path / dtype, max_tokens=128, page_size=16)
+        rep.run_stream(json.dumps(s) for s in steps)
+        rep.cache.check()
+        compare(steps, tmp_path / dtype, c["vocab"], want, dtype, case="loselix drawn at random")
