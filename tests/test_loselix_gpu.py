@@ -598,8 +598,8 @@ def random_configuration(seed):
     """A configuration drawn at random: every size, the order of the layers, the loop and which options are there."""
     import random
     rng = random.Random(seed)
-    width = rng.choice([40, 64, 72, 96, 128, 136])
-    sizes = [8, 16, 24, 32, 48, 64, 80, 96, 128]
+    width = rng.choice([40, 50, 64, 72, 100, 128, 136])
+    sizes = [6, 8, 16, 20, 32, 48, 64, 80, 96, 128]
     layers = []
     for _ in range(rng.randint(1, 5)):
         kv = rng.choice([1, 2, 3])
@@ -622,7 +622,7 @@ def random_configuration(seed):
     return config(rng.choice([97, 160, 333]), width, layers, eps=rng.choice([1e-6, 1e-5]), loop=loop)
 
 
-@pytest.mark.parametrize("seed", range(8))
+@pytest.mark.parametrize("seed", range(10))
 def test_configurations_drawn_at_random(seed, tmp_path):
     """Sizes, layer orders, loops and options that nobody chose: portions of changing size, then single tokens, two
     requests side by side, in both precisions."""
